@@ -1,0 +1,285 @@
+"""`beam._C` — the kernel registry of BEAM, bound to the B200 C-ABI library.
+
+The reference builds a pybind11 module `beam_C` whose functions take torch tensors
+(cuda/main.cc:51-60; signatures in python/beam/_C/beam_C.pyi:3-23) and re-exports it from
+python/beam/_C/__init__.py.  Here the same names, argument names, defaults and in-place `c` are kept,
+but each function is a thin ctypes call into libbeam_b200.so: tensors are checked, reduced to raw device
+pointers and sizes, and launched on torch's current CUDA stream.  Errors become Python exceptions
+(the reference exits the process or silently does nothing), which is what `Operator.check_callable`
+needs to reject a candidate.
+
+There is no CPU path: importing works anywhere (so the API can be inspected), but every kernel call
+raises unless libbeam_b200.so is built and the tensors live on an sm_100 device.
+"""
+import ctypes
+import os
+
+import torch
+
+__all__ = [
+    "cublas_gemmexrc",
+    "cublas_hgemmrc",
+    "cutlass_gemmrc",
+    "cutlass_gemmrc_spec",
+    "cutlass_gemmrc_splitk",
+    "cutlass_gemmrc_splitk_spec",
+    "custom_gemmrc_128x128",
+    "custom_gemmrc_128x256",
+    "cutlass_parallel_gemmrc_lnr",
+    "gemmrc",
+    "gemmrc_host",
+    "BeamError",
+    "library_path",
+]
+
+_PKG = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_LIB_PATH = os.path.join(_PKG, "libbeam_b200.so")
+_lib = None
+
+BEAM_OK = 0
+_VALUE_ERRORS = (1, 2, 3, 4)  # invalid argument, unsupported, alignment, workspace
+
+
+class BeamError(RuntimeError):
+    """A kernel could not be launched or reported a device fault."""
+
+
+class beam_gemm_cfg(ctypes.Structure):
+    _fields_ = [
+        ("tile_n", ctypes.c_int),
+        ("cta_pair", ctypes.c_int),
+        ("stages", ctypes.c_int),
+        ("group_m", ctypes.c_int),
+        ("split_k_slices", ctypes.c_int),
+        ("max_ctas", ctypes.c_int),
+        ("reserved", ctypes.c_int * 2),
+    ]
+
+
+def library_path():
+    return _LIB_PATH
+
+
+def _load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise BeamError(
+            "libbeam_b200.so is not built (%s); run `python %s` — there is no fallback path"
+            % (_LIB_PATH, os.path.join(_PKG, "build.py")))
+    L = ctypes.CDLL(_LIB_PATH)
+    vp, i, f, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+    L.beam_status_string.restype = ctypes.c_char_p
+    L.beam_status_string.argtypes = [i]
+    L.beam_last_cuda_error.restype = ctypes.c_char_p
+    L.beam_version.restype = ctypes.c_char_p
+    L.beam_device_status.argtypes = [i, ctypes.POINTER(i)]
+    L.beam_gemmrc_fp16.argtypes = [vp, vp, vp, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp]
+    for name in ("beam_custom_gemmrc_128x128", "beam_custom_gemmrc_128x256", "beam_cutlass_gemmrc"):
+        getattr(L, name).argtypes = [vp, vp, vp, i, i, i, vp]
+    L.beam_cutlass_gemmrc_spec.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp]
+    L.beam_gemmrc_splitk_workspace_bytes.restype = sz
+    L.beam_gemmrc_splitk_workspace_bytes.argtypes = [i, i, i, i, i]
+    L.beam_gemmrc_splitk_heuristic.argtypes = [i, i, i, i]
+    L.beam_cutlass_gemmrc_splitk.argtypes = [vp, vp, vp, i, i, i, i, vp, sz, vp]
+    L.beam_cutlass_gemmrc_splitk_spec.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, vp, sz, vp]
+    L.beam_gemmrc_layernorm_workspace_bytes.restype = sz
+    L.beam_gemmrc_layernorm_workspace_bytes.argtypes = [i, i, i]
+    L.beam_gemmrc_layernorm.argtypes = [vp, vp, vp, vp, vp, f, i, i, i, vp, sz, vp]
+    L.beam_gemmrc_fp16_host.argtypes = [vp, vp, vp, i, i, i]
+    _lib = L
+    return L
+
+
+def _raise(status, what):
+    L = _load()
+    msg = "%s: %s" % (what, L.beam_status_string(status).decode())
+    if status in (5, 6, 8):
+        detail = L.beam_last_cuda_error().decode()
+        if detail:
+            msg += " [%s]" % detail
+    if status in _VALUE_ERRORS:
+        raise ValueError(msg)
+    raise BeamError(msg)
+
+
+def _check_abc(a, b, c):
+    """Same preconditions as the reference's checkTensor / checkIntEqual / fp16 dispatch
+    (cuda/include/torch_utils.h:7-47, cuda/cutlass_kernels/main.cc:25-45), reported as exceptions."""
+    for name, t in (("a", a), ("b", b), ("c", c)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError("%s must be a torch.Tensor" % name)
+        if not t.is_cuda:
+            raise ValueError("%s must be a CUDA tensor (there is no CPU path)" % name)
+        if not t.is_contiguous():
+            raise ValueError("%s must be contiguous" % name)
+        if t.dtype != torch.float16:
+            raise TypeError("%s must be float16, got %s" % (name, t.dtype))
+        if t.dim() != 2:
+            raise ValueError("%s must be 2-D" % name)
+    if not (a.device == b.device == c.device):
+        raise ValueError("a, b, c must be on the same device")
+    m, k = a.shape
+    n, kb = b.shape
+    if k != kb:
+        raise ValueError("a is [M,K]=%s but b is [N,K]=%s" % (tuple(a.shape), tuple(b.shape)))
+    if tuple(c.shape) != (m, n):
+        raise ValueError("c must be [M,N]=(%d,%d), got %s" % (m, n, tuple(c.shape)))
+    return int(m), int(n), int(k)
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    """Grow-only scratch tensor per device, owned by the binding (the reference hides a cudaMalloc'd
+    buffer inside the extension instead: cutlass_gemmrc_splitk.cu:31-42)."""
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _run(fn_name, a, b, c, *extra):
+    m, n, k = _check_abc(a, b, c)
+    L = _load()
+    with torch.cuda.device(a.device):
+        st = getattr(L, fn_name)(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, *extra, _stream(a))
+    if st != BEAM_OK:
+        _raise(st, fn_name)
+
+
+def custom_gemmrc_128x128(a, b, c):
+    """c[M,N] = a[M,K] @ b[N,K].T with 128x128 tiles (registry slot of cute_gemm_128x128.cu)."""
+    _run("beam_custom_gemmrc_128x128", a, b, c)
+
+
+def custom_gemmrc_128x256(a, b, c):
+    """c = a @ b.T with 128x256 tiles (registry slot of cute_gemm_128x256.cu)."""
+    _run("beam_custom_gemmrc_128x256", a, b, c)
+
+
+def cutlass_gemmrc(a, b, c):
+    """c = a @ b.T, library default: 256x256 tile on a CTA pair (slot of cutlass_gemmrc.cu:21-40)."""
+    _run("beam_cutlass_gemmrc", a, b, c)
+
+
+def _pair(v, name):
+    v = list(v)
+    if len(v) != 2:
+        raise ValueError("%s must have two entries" % name)
+    return int(v[0]), int(v[1])
+
+
+def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64]):
+    """c = a @ b.T with the tile family named by shape_threadblock: [128,128], [128,256] (one CTA per
+    tile) or [256,128], [256,256] (CTA pair).  shape_warp is kept for signature compatibility
+    (cuda/cutlass_kernels/main.cc:129-132) and ignored."""
+    tbm, tbn = _pair(shape_threadblock, "shape_threadblock")
+    wm, wn = _pair(shape_warp, "shape_warp")
+    _run("beam_cutlass_gemmrc_spec", a, b, c, tbm, tbn, wm, wn)
+
+
+def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0):
+    """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over."""
+    m, n, k = _check_abc(a, b, c)
+    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas))
+    L = _load()
+    with torch.cuda.device(a.device):
+        st = L.beam_gemmrc_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg), _stream(a))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_fp16")
+
+
+def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0):
+    """Split-K c = a @ b.T for small M, N and huge K; fp32 partials summed in slice order (bitwise
+    reproducible).  split_k_slices = 0 lets the library choose (slot of cutlass_gemmrc_splitk.cu:59-105)."""
+    m, n, k = _check_abc(a, b, c)
+    L = _load()
+    with torch.cuda.device(a.device):
+        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, 0, int(split_k_slices))
+        ws = _workspace(a.device, nbytes)
+        st = L.beam_cutlass_gemmrc_splitk(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, int(split_k_slices),
+                                          ws.data_ptr(), ws.numel(), _stream(a))
+    if st != BEAM_OK:
+        _raise(st, "beam_cutlass_gemmrc_splitk")
+
+
+def cutlass_gemmrc_splitk_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64], split_k_slices=0):
+    """Split-K with the tile's N taken from shape_threadblock[1] (64, 128 or 256)."""
+    m, n, k = _check_abc(a, b, c)
+    tbm, tbn = _pair(shape_threadblock, "shape_threadblock")
+    wm, wn = _pair(shape_warp, "shape_warp")
+    L = _load()
+    with torch.cuda.device(a.device):
+        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, tbn, int(split_k_slices))
+        ws = _workspace(a.device, nbytes)
+        st = L.beam_cutlass_gemmrc_splitk_spec(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, tbm, tbn, wm, wn,
+                                               int(split_k_slices), ws.data_ptr(), ws.numel(), _stream(a))
+    if st != BEAM_OK:
+        _raise(st, "beam_cutlass_gemmrc_splitk_spec")
+
+
+def cutlass_parallel_gemmrc_lnr(a, b, c, gamma, beta, eps=1e-5):
+    """Fused GEMM + LayerNorm: c[M,N] = LayerNorm_rows(a[M,K] @ b[N,K].T) * gamma[N] + beta[N].
+
+    Keeps the reference's registry slot and five-tensor arity (cuda/cute_kernels/main.cc:55-76,87), but
+    the last two tensors are LayerNorm's gamma and beta rather than the input/output of the unrelated
+    SiLU that the reference kernel runs beside its GEMM (cute_gemm_ln.cu:127-198)."""
+    m, n, k = _check_abc(a, b, c)
+    for name, t in (("gamma", gamma), ("beta", beta)):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous() and t.dtype == torch.float16):
+            raise TypeError("%s must be a contiguous CUDA float16 tensor" % name)
+        if t.numel() != n:
+            raise ValueError("%s must have N=%d elements" % (name, n))
+    L = _load()
+    with torch.cuda.device(a.device):
+        nbytes = L.beam_gemmrc_layernorm_workspace_bytes(m, n, k)
+        ws = _workspace(a.device, nbytes)
+        st = L.beam_gemmrc_layernorm(a.data_ptr(), b.data_ptr(), c.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                     float(eps), m, n, k, ws.data_ptr(), ws.numel(), _stream(a))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_layernorm")
+
+
+def gemmrc_host(a, b, c):
+    """a, b, c are CPU float16 tensors (ideally pinned): copies in, multiplies on the current CUDA device,
+    copies c back; returns when c is complete."""
+    for name, t in (("a", a), ("b", b), ("c", c)):
+        if not (isinstance(t, torch.Tensor) and not t.is_cuda and t.is_contiguous() and t.dtype == torch.float16):
+            raise TypeError("%s must be a contiguous CPU float16 tensor" % name)
+    m, k = a.shape
+    n, kb = b.shape
+    if k != kb or tuple(c.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    st = _load().beam_gemmrc_fp16_host(a.data_ptr(), b.data_ptr(), c.data_ptr(), int(m), int(n), int(k))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_fp16_host")
+
+
+def device_status(clear=False):
+    """(status, fault_word) of the current device; synchronises it."""
+    word = ctypes.c_int(0)
+    st = _load().beam_device_status(1 if clear else 0, ctypes.byref(word))
+    return st, word.value
+
+
+# ---- cuBLAS comparators (baselines only; kept because the tuner and the driver list them) ---------
+def cublas_gemmexrc(a, b, c):
+    """cuBLAS GemmEx with fp32 compute via torch (reference: cuda/cublas.cc:93-122). Comparison baseline."""
+    _check_abc(a, b, c)
+    torch.matmul(a, b.t(), out=c)
+
+
+def cublas_hgemmrc(a, b, c):
+    """cuBLAS Hgemm slot (reference: cuda/cublas.cc:44-71).  torch exposes one fp16 matmul; whether it
+    accumulates in fp16 is governed by torch.backends.cuda.matmul.allow_fp16_accumulation."""
+    _check_abc(a, b, c)
+    torch.matmul(a, b.t(), out=c)

@@ -1,0 +1,262 @@
+// Host launchers of the persistent UMMA kernels: validate the problem, pick the kernel
+// instantiation named by the plan, build the TMA descriptors and launch on the caller's stream.
+#include "gemmrc_launch.h"
+
+#include "gemmrc_umma.cuh"
+#include "layernorm_launch.h"
+#include "splitk_launch.h"
+
+namespace beam {
+
+namespace {
+
+struct ExtraArgs {
+  float* scratch = nullptr;
+  const __half* gamma = nullptr;
+  const __half* beta = nullptr;
+  float eps = 0.f;
+  int slices = 1;
+};
+
+template <int BN, int kStages, int kCta, int kMode>
+int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
+                    int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
+  using S = GemmShape<BN, kStages, kCta>;
+  auto kernel = gemmrc_umma_kernel<BN, kStages, kCta, kMode>;
+
+  // One-time per (instantiation, device): opt in to the large dynamic shared memory and, for
+  // pairs, ask how many 2-CTA clusters fit on this part at once.
+  static int configured_clusters[64] = {0};
+  int& resident = configured_clusters[ctx->device];
+  if (resident == 0) {
+    if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
+    BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
+                  "cudaFuncSetAttribute(smem)");
+    int clusters = ctx->sm_count / kCta;
+    if (kCta == 2) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(static_cast<unsigned>(ctx->sm_count / 2 * 2), 1, 1);
+      probe.blockDim = dim3(S::kThreads, 1, 1);
+      probe.dynamicSmemBytes = S::kSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      probe.attrs = attr;
+      probe.numAttrs = 1;
+      int n_clusters = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, kernel, &probe);
+      if (e == cudaSuccess && n_clusters > 0 && n_clusters < clusters) clusters = n_clusters;
+      (void)cudaGetLastError();
+    }
+    resident = clusters > 0 ? clusters : 1;
+  }
+
+  GemmParams p;
+  int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                          static_cast<uint64_t>(k), S::kBM, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                      S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  p.c = static_cast<__half*>(C);
+  p.scratch = ex.scratch;
+  p.gamma = ex.gamma;
+  p.beta = ex.beta;
+  p.eps = ex.eps;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ldc = n;
+  const int tile_m = S::kBM * kCta;
+  p.m_tiles = (m + tile_m - 1) / tile_m;
+  p.n_tiles = (n + BN - 1) / BN;
+  p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 8 : 16);
+  p.slices = ex.slices;
+  p.status = ctx->status_word;
+
+  long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
+  if (kMode == kModeLayerNorm) items = p.m_tiles;  // a CTA (pair) owns whole row panels
+  int clusters = resident;
+  if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
+  if (items < clusters) clusters = static_cast<int>(items);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCta), 1, 1);
+  cfg.blockDim = dim3(S::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCta;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
+  return BEAM_OK;
+}
+
+}  // namespace
+
+int default_stages(int bn, int cta) {
+  if (cta == 2) return bn == 256 ? 6 : 8;
+  return bn == 256 ? 4 : (bn == 128 ? 6 : 8);
+}
+
+int validate_gemm_args(const void* A, const void* B, const void* C, int m, int n, int k) {
+  if (!A || !B || !C) return BEAM_ERR_INVALID_ARG;
+  if (m <= 0 || n <= 0 || k <= 0) return BEAM_ERR_INVALID_ARG;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return BEAM_ERR_ALIGNMENT;
+  if ((k % 8) != 0 || (n % 8) != 0) return BEAM_ERR_ALIGNMENT;
+  return BEAM_OK;
+}
+
+// ------------------------------------------------------------------------------- large GEMM
+#define BEAM_GEMM_CASE(BN_, ST_, CTA_)                                                \
+  if (plan.tile_n == BN_ && stages == ST_ && plan.cta_pair == CTA_)                   \
+    return launch_instance<BN_, ST_, CTA_, kModeGemm>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, \
+                                                      stream);
+
+int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
+                  cudaStream_t stream) {
+  int st = validate_gemm_args(A, B, C, m, n, k);
+  if (st != BEAM_OK) return st;
+  DeviceCtx* ctx = current_device_ctx(&st);
+  if (!ctx) return st;
+  const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
+  const ExtraArgs ex;
+  BEAM_GEMM_CASE(256, 4, 2)
+  BEAM_GEMM_CASE(256, 5, 2)
+  BEAM_GEMM_CASE(256, 6, 2)
+  BEAM_GEMM_CASE(256, 7, 2)
+  BEAM_GEMM_CASE(128, 4, 2)
+  BEAM_GEMM_CASE(128, 6, 2)
+  BEAM_GEMM_CASE(128, 8, 2)
+  BEAM_GEMM_CASE(256, 3, 1)
+  BEAM_GEMM_CASE(256, 4, 1)
+  BEAM_GEMM_CASE(128, 4, 1)
+  BEAM_GEMM_CASE(128, 6, 1)
+  BEAM_GEMM_CASE(128, 7, 1)
+  BEAM_GEMM_CASE(64, 4, 1)
+  BEAM_GEMM_CASE(64, 8, 1)
+  return BEAM_ERR_UNSUPPORTED;
+}
+#undef BEAM_GEMM_CASE
+
+// ---------------------------------------------------------------------------------- split-K
+int splitk_tile_n(int n, int tile_n) {
+  if (tile_n == 64 || tile_n == 128 || tile_n == 256) return tile_n;
+  return n <= 64 ? 64 : 128;
+}
+
+// One work item per SM: slices = SMs / tiles, but never fewer than 4 k-blocks (256 of K) per slice,
+// so that the fill of the TMA ring is amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:
+// 44-57, targets the 108 SMs of an A100 and rounds to half waves.)
+int splitk_heuristic(int m, int n, int k, int tile_n) {
+  const int bn = splitk_tile_n(n, tile_n);
+  const long long tiles = static_cast<long long>((m + 127) / 128) * ((n + bn - 1) / bn);
+  const int num_kb = (k + 63) / 64;
+  int sms = 148;
+  int err = 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    if (DeviceCtx* ctx = current_device_ctx(&err)) sms = ctx->sm_count;
+  } else {
+    (void)cudaGetLastError();
+  }
+  long long s = sms / (tiles > 0 ? tiles : 1);
+  const long long cap = num_kb / 4 > 0 ? num_kb / 4 : 1;
+  if (s > cap) s = cap;
+  if (s > 256) s = 256;
+  if (s < 1) s = 1;
+  return static_cast<int>(s);
+}
+
+int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested) {
+  const int num_kb = (k + 63) / 64;
+  if (requested > 0 && requested <= num_kb && requested <= 1024) return requested;
+  return splitk_heuristic(m, n, k, tile_n);
+}
+
+size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const int s = splitk_resolve_slices(m, n, k, tile_n, slices);
+  return static_cast<size_t>(s) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+}
+
+int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, int tile_n, int slices,
+                  void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  int st = validate_gemm_args(A, B, C, m, n, k);
+  if (st != BEAM_OK) return st;
+  if (slices < 0) return BEAM_ERR_INVALID_ARG;
+  if (m > 65535) return BEAM_ERR_UNSUPPORTED;  // the reduction grid has one block row per output row
+  DeviceCtx* ctx = current_device_ctx(&st);
+  if (!ctx) return st;
+  const int bn = splitk_tile_n(n, tile_n);
+  const int s = splitk_resolve_slices(m, n, k, bn, slices);
+  const size_t need = static_cast<size_t>(s) * m * n * sizeof(float);
+  if (!workspace || workspace_bytes < need) return BEAM_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
+
+  ExtraArgs ex;
+  ex.scratch = static_cast<float*>(workspace);
+  ex.slices = s;
+  if (bn == 64)
+    st = launch_instance<64, 8, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+  else if (bn == 128)
+    st = launch_instance<128, 6, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+  else
+    st = launch_instance<256, 4, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+  if (st != BEAM_OK) return st;
+
+  // Fixed-order reduction, launched so that its blocks may become resident while the partial
+  // kernel drains; it blocks in griddepcontrol.wait until every partial is written and visible.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((n + 127) / 128), static_cast<unsigned>(m), 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float*>(workspace),
+                                   static_cast<__half*>(C), m, n, s),
+                "cudaLaunchKernelEx(splitk_reduce)");
+  return BEAM_OK;
+}
+
+// ------------------------------------------------------------------------ GEMM + LayerNorm
+size_t layernorm_workspace_bytes(int m, int n, int k) {
+  (void)k;
+  if (m <= 0 || n <= 0) return 0;
+  return static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+}
+
+int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* gamma, const void* beta, float eps,
+                          int m, int n, int k, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  int st = validate_gemm_args(X, W, out, m, n, k);
+  if (st != BEAM_OK) return st;
+  if (!gamma || !beta || !(eps >= 0.f)) return BEAM_ERR_INVALID_ARG;
+  if (!aligned16(gamma) || !aligned16(beta)) return BEAM_ERR_ALIGNMENT;
+  if (!workspace || workspace_bytes < layernorm_workspace_bytes(m, n, k)) return BEAM_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
+  DeviceCtx* ctx = current_device_ctx(&st);
+  if (!ctx) return st;
+  ExtraArgs ex;
+  ex.scratch = static_cast<float*>(workspace);
+  ex.gamma = static_cast<const __half*>(gamma);
+  ex.beta = static_cast<const __half*>(beta);
+  ex.eps = eps;
+  // Pair panels of 256 rows once there are enough of them to fill the device; otherwise 128-row
+  // panels on single CTAs keep more SMs busy.
+  const int pair_panels = (m + 255) / 256;
+  if (pair_panels >= ctx->sm_count / 4)
+    return launch_instance<256, 6, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, 1, 0, ex, stream);
+  return launch_instance<256, 4, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, 1, 0, ex, stream);
+}
+
+}  // namespace beam

@@ -1,0 +1,21 @@
+// Launcher interface of the persistent UMMA kernels (implementation: gemmrc_launch.cu).
+#pragma once
+
+#include "host_common.h"
+
+namespace beam {
+
+struct GemmPlan {
+  int tile_n = 256;   // UMMA N
+  int cta_pair = 2;   // 1 or 2 CTAs per tile
+  int stages = 0;     // 0 = deepest ring that fits
+  int group_m = 0;    // 0 = default rasterisation group
+  int max_ctas = 0;   // 0 = whole device
+};
+
+int default_stages(int tile_n, int cta_pair);
+int validate_gemm_args(const void* A, const void* B, const void* C, int m, int n, int k);
+int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
+                  cudaStream_t stream);
+
+}  // namespace beam

@@ -1,0 +1,106 @@
+// Per-device context and TMA descriptor encoding for the beam_b200 library.
+#include "host_common.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace beam {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_ctx_mutex;
+
+thread_local char t_cuda_error[256] = "";
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime so the library carries no link-time
+// dependency on libcuda (it must load, and export its symbols, on a machine without a GPU).
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+void note_cuda_error(cudaError_t e, const char* where) {
+  std::snprintf(t_cuda_error, sizeof(t_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+}
+const char* last_cuda_error_text() { return t_cuda_error; }
+
+DeviceCtx* current_device_ctx(int* err) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    if (e != cudaSuccess) note_cuda_error(e, "cudaGetDevice");
+    (void)cudaGetLastError();
+    *err = BEAM_ERR_NO_DEVICE;
+    return nullptr;
+  }
+  DeviceCtx* c = &g_ctx[dev];
+  if (c->ok) return c;
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  if (c->ok) return c;
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) {
+    note_cuda_error(e, "cudaGetDeviceProperties");
+    (void)cudaGetLastError();
+    *err = BEAM_ERR_NO_DEVICE;
+    return nullptr;
+  }
+  if (prop.major != 10) {  // the kernels are built for sm_100a only
+    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "device %d is sm_%d%d, need sm_100", dev, prop.major,
+                  prop.minor);
+    *err = BEAM_ERR_NO_DEVICE;
+    return nullptr;
+  }
+  c->device = dev;
+  c->sm_count = prop.multiProcessorCount;
+  c->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+  c->cc_major = prop.major;
+  c->cc_minor = prop.minor;
+  e = cudaMalloc(&c->status_word, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, 256);
+  if (e != cudaSuccess) {
+    note_cuda_error(e, "status word");
+    (void)cudaGetLastError();
+    *err = BEAM_ERR_CUDA;
+    return nullptr;
+  }
+  c->ok = true;
+  return c;
+}
+
+int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                   uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return BEAM_ERR_TENSORMAP;
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled failed with CUresult %d",
+                  static_cast<int>(r));
+    return BEAM_ERR_TENSORMAP;
+  }
+  return BEAM_OK;
+}
+
+}  // namespace beam

@@ -1,0 +1,50 @@
+// Host-side plumbing shared by the launchers: the per-device context (SM count, fault word;
+// its one allocation happens at first use of a device), CUDA error bookkeeping, and the TMA
+// tensor-map encoder fetched from the driver at run time.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/beam_b200.h"
+
+namespace beam {
+
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int cc_major = 0, cc_minor = 0;
+  int* status_word = nullptr;  // device memory, one int, zero while healthy
+  bool ok = false;
+};
+
+// Returns the context of the CUDA device that is current on the calling thread, creating it
+// on first use (cudaMalloc of the 4-byte status word happens there, never on a later call).
+// On failure returns nullptr and stores a BEAM_ERR_* code in *err.
+DeviceCtx* current_device_ctx(int* err);
+
+// 2-D row-major fp16/fp32 tensor map: `rows` x `cols` elements, row pitch `ld` elements,
+// box = box_rows x box_cols, 128-byte swizzle when swizzle128 is set (box_cols * elem = 128 B).
+int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                   uint32_t box_rows, uint32_t box_cols, bool swizzle128);
+
+// Records a CUDA runtime failure for beam_last_cuda_error() (thread-local text).
+void note_cuda_error(cudaError_t e, const char* where);
+const char* last_cuda_error_text();
+
+#define BEAM_CUDA_TRY(expr, where)            \
+  do {                                        \
+    cudaError_t _e = (expr);                  \
+    if (_e != cudaSuccess) {                  \
+      ::beam::note_cuda_error(_e, where);     \
+      (void)cudaGetLastError();               \
+      return BEAM_ERR_CUDA;                   \
+    }                                         \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace beam

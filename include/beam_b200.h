@@ -1,0 +1,151 @@
+/* beam_b200 — C ABI of the B200 (sm_100a) kernels behind BEAM's fp16 "rc" GEMM registry.
+ *
+ * rc GEMM:  C[M,N] (fp16, row-major) = A[M,K] (fp16, row-major) x B[N,K]^T (B stored [N,K], i.e.
+ * column-major KxN), fp32 accumulation, one round-to-nearest-even to fp16 at the end, alpha = 1,
+ * beta = 0.  (Reference semantics: cuda/cute_kernels/main.cc:29-40, cute_gemm_128x128.cu:89-92,183,
+ * cuda/cutlass_kernels/cutlass_gemmrc.cu:22-30.)
+ *
+ * Conventions for every entry point:
+ *   - all pointers are DEVICE pointers on the CUDA device current on the calling thread, unless a
+ *     parameter is documented as host memory; A, B, C and workspace must be 16-byte aligned;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream); calls are
+ *     asynchronous with respect to the host and re-entrant across streams;
+ *   - the return value is a BEAM_* status; nothing here ever calls exit() or throws.  The reference's
+ *     entry functions return void and exit(-1) / std::terminate / silently do nothing on error
+ *     (cuda/include/cuda_utils.h:7-23, torch_utils.h:7-37, cutlass_gemmrc.cu:33-37);
+ *   - shapes: K % 8 == 0 and N % 8 == 0 (16-byte rows for TMA); M, N, K need not be tile multiples
+ *     (out-of-range tile parts are zero-filled on load and masked on store).
+ *   - device-pointer entry points allocate nothing after the first call on a device (that call
+ *     creates a small fault word); split-K and LayerNorm scratch is caller-provided.
+ */
+#ifndef BEAM_B200_H_
+#define BEAM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define BEAM_API __attribute__((visibility("default")))
+#else
+#define BEAM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BEAM_OK 0
+#define BEAM_ERR_INVALID_ARG 1     /* null pointer, non-positive size, bad enum */
+#define BEAM_ERR_UNSUPPORTED 2     /* shape / tile / split factor this build cannot run */
+#define BEAM_ERR_ALIGNMENT 3       /* pointer not 16-byte aligned or K, N not multiples of 8 */
+#define BEAM_ERR_WORKSPACE 4       /* workspace missing or too small */
+#define BEAM_ERR_CUDA 5            /* a CUDA runtime call failed (see beam_last_cuda_error) */
+#define BEAM_ERR_TENSORMAP 6       /* the driver refused a TMA descriptor */
+#define BEAM_ERR_DEVICE_TIMEOUT 7  /* a kernel's bounded wait ran out (see beam_device_status) */
+#define BEAM_ERR_NO_DEVICE 8       /* no sm_100 device is current */
+
+/* Blackwell tuning knobs; zero in any field means "library default".  This is what replaces the
+ * reference's shape_threadblock / shape_warp vectors (cuda/cutlass_kernels/main.cc:129-141) in
+ * the auto-tuner's search space. */
+typedef struct beam_gemm_cfg {
+  int tile_n;         /* UMMA N per output tile: 64, 128 or 256                               */
+  int cta_pair;       /* 1 = one CTA per 128-row tile; 2 = cta_group::2 pair on a 256-row tile */
+  int stages;         /* depth of the TMA->UMMA shared-memory ring (2..8)                      */
+  int group_m;        /* tile rasterisation: M-tiles per L2 group                              */
+  int split_k_slices; /* split-K only: number of K slices (0 = heuristic)                      */
+  int max_ctas;       /* cap on the persistent grid (0 = all SMs)                              */
+  int reserved[2];
+} beam_gemm_cfg;
+
+BEAM_API const char* beam_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+BEAM_API const char* beam_last_cuda_error(void);
+/* Library build tag, e.g. "beam_b200 sm_100a". */
+BEAM_API const char* beam_version(void);
+
+/* Reads the current device's fault word (synchronises the device). 0 = healthy.  Non-zero values
+ * are DeviceFault codes written by a kernel whose bounded wait expired. `clear` != 0 resets it. */
+BEAM_API int beam_device_status(int clear, int* fault_word_out);
+
+/* ---- large rc GEMM -------------------------------------------------------------------------- */
+
+/* Generic entry: persistent warp-specialised TMA + tcgen05 kernel, configuration from cfg (NULL =
+ * defaults).  Everything below is a named preset of this. */
+BEAM_API int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k, const beam_gemm_cfg* cfg,
+                     void* stream);
+
+/* Registry name `custom_gemmrc_128x128` — replaces entry_custom_gemmrc_128x128
+ * (cuda/cute_kernels/cute_gemm_128x128.cu:193-205, declared cuda/cute_kernels/main.cc:13-14):
+ * 128x128 output tile per CTA. */
+BEAM_API int beam_custom_gemmrc_128x128(const void* A, const void* B, void* C, int m, int n, int k, void* stream);
+
+/* Registry name `custom_gemmrc_128x256` — replaces entry_custom_gemmrc_128x256
+ * (cuda/cute_kernels/cute_gemm_128x256.cu:196-208, declared cuda/cute_kernels/main.cc:15-16):
+ * 128x256 output tile per CTA. */
+BEAM_API int beam_custom_gemmrc_128x256(const void* A, const void* B, void* C, int m, int n, int k, void* stream);
+
+/* Registry name `cutlass_gemmrc` — replaces entry_cutlass_gemmrc (cuda/cutlass_kernels/
+ * cutlass_gemmrc.cu:21-40): the library's best default, a 256x256 tile on a CTA pair. */
+BEAM_API int beam_cutlass_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, void* stream);
+
+/* Registry name `cutlass_gemmrc_spec` — replaces entry_cutlass_gemmrc_spec (cuda/cutlass_kernels/
+ * cutlass_gemmrc.cu:55-111).  shape_threadblock = {tb_m, tb_n} selects the tile family:
+ * {128,128}, {128,256} -> one CTA per tile; {256,128}, {256,256} -> CTA pair.  shape_warp is accepted
+ * for signature compatibility and ignored (a UMMA has no warp tile).  Unlike the reference, an
+ * unknown shape returns BEAM_ERR_UNSUPPORTED instead of silently doing nothing (:73-80). */
+BEAM_API int beam_cutlass_gemmrc_spec(const void* A, const void* B, void* C, int m, int n, int k, int tb_m, int tb_n,
+                             int warp_m, int warp_n, void* stream);
+
+/* ---- split-K rc GEMM for small M, N and huge K ------------------------------------------------ */
+
+/* Scratch bytes the split-K entry points need: fp32 partials [slices][M][N] (the layout of the
+ * reference's CUTLASS workspace).  tile_n = 0 and split_k_slices = 0 mean "what the library would
+ * pick"; pass the same values as to the entry point. */
+BEAM_API size_t beam_gemmrc_splitk_workspace_bytes(int m, int n, int k, int tile_n, int split_k_slices);
+
+/* The split factor the heuristic picks for this tile_n (0 = default tile): one work item per SM, at
+ * least 256 of K per slice.  Replaces get_slice_heuristic (cuda/cutlass_kernels/
+ * cutlass_gemmrc_splitk.cu:44-57), which models the 108 SMs of an A100. */
+BEAM_API int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n);
+
+/* Registry name `cutlass_gemmrc_splitk` — replaces entry_cutlass_gemmrc_splitk (cuda/cutlass_kernels/
+ * cutlass_gemmrc_splitk.cu:59-105).  K is cut into `split_k_slices` contiguous runs of 64-wide
+ * k-blocks; each CTA accumulates one slice of one tile in TMEM and writes an fp32 partial to
+ * `workspace`; a second kernel adds the partials of every output in a fixed order that depends only
+ * on the slice count (bitwise reproducible) and rounds once to fp16.  A split factor outside
+ * [1, K/64] falls back to the heuristic, as the reference does for values outside (0, K/32) (:77-94).
+ * The reference keeps a hidden grow-only cudaMalloc'd buffer (:31-42); here the caller owns it. */
+BEAM_API int beam_cutlass_gemmrc_splitk(const void* A, const void* B, void* C, int m, int n, int k, int split_k_slices,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Registry name `cutlass_gemmrc_splitk_spec` — replaces entry_cutlass_gemmrc_splitk_spec
+ * (cuda/cutlass_kernels/cutlass_gemmrc_splitk.cu:107-195).  tb_n selects the UMMA N of the tile
+ * (64, 128 or 256); tb_m and shape_warp are accepted and ignored (tiles are always 128 rows, rows
+ * beyond M are zero-filled). */
+BEAM_API int beam_cutlass_gemmrc_splitk_spec(const void* A, const void* B, void* C, int m, int n, int k, int tb_m,
+                                    int tb_n, int warp_m, int warp_n, int split_k_slices, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+/* ---- fused GEMM + LayerNorm --------------------------------------------------------------------- */
+
+/* Scratch bytes for beam_gemmrc_layernorm: fp32 row statistics exchanged between the N-tiles. */
+BEAM_API size_t beam_gemmrc_layernorm_workspace_bytes(int m, int n, int k);
+
+/* Registry slot `cutlass_parallel_gemmrc_lnr` (cuda/cute_kernels/main.cc:55-76,87; the reference
+ * kernel behind it, cute_gemm_ln.cu:24-245, is a GEMM next to an unrelated SiLU and has no LayerNorm).
+ * out[M,N] = LayerNorm_row( X[M,K] x W[N,K]^T ) * gamma[N] + beta[N]: mean and population variance per
+ * output row in fp32 from the fp32 accumulators, rstd = rsqrt(var + eps), result rounded once to fp16. */
+BEAM_API int beam_gemmrc_layernorm(const void* X, const void* W, void* out, const void* gamma, const void* beta, float eps,
+                          int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- host-buffer convenience (what a caller with pageable or pinned HOST arrays uses) ---------- */
+
+/* A, B, C are HOST pointers. Copies A and B to the device in row blocks, runs beam_cutlass_gemmrc on
+ * each block as it lands and copies C back, overlapping the three on separate streams; blocks until
+ * C is complete.  Device staging buffers are allocated on the first call and reused while they fit. */
+BEAM_API int beam_gemmrc_fp16_host(const void* A_host, const void* B_host, void* C_host, int m, int n, int k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BEAM_B200_H_ */
