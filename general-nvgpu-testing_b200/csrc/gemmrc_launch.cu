@@ -16,6 +16,8 @@ struct ExtraArgs {
   const __half* beta = nullptr;
   float eps = 0.f;
   int slices = 1;
+  float2* row_part = nullptr;
+  int* tickets = nullptr;
 };
 
 template <int BN, int kStages, int kCta, int kMode>
@@ -62,6 +64,8 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   if (st != BEAM_OK) return st;
   p.c = static_cast<__half*>(C);
   p.scratch = ex.scratch;
+  p.row_part = ex.row_part;
+  p.tickets = ex.tickets;
   p.gamma = ex.gamma;
   p.beta = ex.beta;
   p.eps = ex.eps;
@@ -76,8 +80,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.slices = ex.slices;
   p.status = ctx->status_word;
 
-  long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
-  if (kMode == kModeLayerNorm) items = p.m_tiles;  // a CTA (pair) owns whole row panels
+  const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
   if (items < clusters) clusters = static_cast<int>(items);
@@ -230,10 +233,30 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
 }
 
 // ------------------------------------------------------------------------ GEMM + LayerNorm
+// Workspace layout: [fp32 panel M x N][(mean, M2) per row per 256-wide N tile][ticket per 128 rows].
+namespace {
+constexpr int kLnTileN = 256;
+struct LnLayout {
+  size_t panel_bytes, part_off, part_bytes, ticket_off, ticket_bytes, total;
+};
+LnLayout ln_layout(int m, int n) {
+  LnLayout l;
+  const size_t n_tiles = static_cast<size_t>((n + kLnTileN - 1) / kLnTileN);
+  const size_t panels = static_cast<size_t>((m + 127) / 128);
+  l.panel_bytes = (static_cast<size_t>(m) * n * sizeof(float) + 255) / 256 * 256;
+  l.part_off = l.panel_bytes;
+  l.part_bytes = (static_cast<size_t>(m) * n_tiles * sizeof(float2) + 255) / 256 * 256;
+  l.ticket_off = l.part_off + l.part_bytes;
+  l.ticket_bytes = (panels * sizeof(int) + 255) / 256 * 256;
+  l.total = l.ticket_off + l.ticket_bytes;
+  return l;
+}
+}  // namespace
+
 size_t layernorm_workspace_bytes(int m, int n, int k) {
   (void)k;
   if (m <= 0 || n <= 0) return 0;
-  return static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+  return ln_layout(m, n).total;
 }
 
 int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* gamma, const void* beta, float eps,
@@ -242,21 +265,25 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   if (st != BEAM_OK) return st;
   if (!gamma || !beta || !(eps >= 0.f)) return BEAM_ERR_INVALID_ARG;
   if (!aligned16(gamma) || !aligned16(beta)) return BEAM_ERR_ALIGNMENT;
-  if (!workspace || workspace_bytes < layernorm_workspace_bytes(m, n, k)) return BEAM_ERR_WORKSPACE;
+  const LnLayout l = ln_layout(m, n);
+  if (!workspace || workspace_bytes < l.total) return BEAM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
+  char* ws = static_cast<char*>(workspace);
   ExtraArgs ex;
-  ex.scratch = static_cast<float*>(workspace);
+  ex.scratch = reinterpret_cast<float*>(ws);
+  ex.row_part = reinterpret_cast<float2*>(ws + l.part_off);
+  ex.tickets = reinterpret_cast<int*>(ws + l.ticket_off);
   ex.gamma = static_cast<const __half*>(gamma);
   ex.beta = static_cast<const __half*>(beta);
   ex.eps = eps;
-  // Pair panels of 256 rows once there are enough of them to fill the device; otherwise 128-row
-  // panels on single CTAs keep more SMs busy.
-  const int pair_panels = (m + 255) / 256;
-  if (pair_panels >= ctx->sm_count / 4)
-    return launch_instance<256, 6, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, 1, 0, ex, stream);
-  return launch_instance<256, 4, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, 1, 0, ex, stream);
+  BEAM_CUDA_TRY(cudaMemsetAsync(ex.tickets, 0, l.ticket_bytes, stream), "cudaMemsetAsync(tickets)");
+  // CTA pairs on 256-row tiles once there are enough tiles to fill the device; single CTAs otherwise.
+  const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + kLnTileN - 1) / kLnTileN);
+  if (pair_tiles >= ctx->sm_count / 2)
+    return launch_instance<kLnTileN, 6, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, 0, 0, ex, stream);
+  return launch_instance<kLnTileN, 4, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, 0, 0, ex, stream);
 }
 
 }  // namespace beam

@@ -21,9 +21,11 @@
 //   kModeGemm       fp32 -> fp16, store C.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
-//   kModeLayerNorm  a CTA (pair) walks one 128(256)-row panel across all N tiles, keeps per-row
-//                   (count, mean, M2) in registers, parks the fp32 tile in a scratch panel, and after
-//                   the last N tile re-reads the panel, normalises, applies gamma/beta, stores fp16.
+//   kModeLayerNorm  tiles are walked in GEMM order (so A and B stay L2-resident).  Each tile's epilogue
+//                   parks its fp32 values in a scratch panel, writes one (mean, M2) pair per row for
+//                   its N range, and takes a ticket for its 128-row panel.  The CTA that draws the last
+//                   ticket of a panel merges the per-tile statistics in tile order, re-reads the panel
+//                   (still in L2), normalises, applies gamma/beta and stores fp16.  Nobody waits.
 #pragma once
 
 #include "umma_common.cuh"
@@ -37,6 +39,8 @@ struct GemmParams {
   CUtensorMap tm_b;  // B  [N, K], box (BN / kCta) x 64, 128 B swizzle
   __half* c;         // fp16 output [M, ldc]
   float* scratch;    // split-K: partials [slices][M][N]; LayerNorm: fp32 panel store [M][N]
+  float2* row_part;  // LayerNorm: (mean, M2) of every row over each N tile, [M][n_tiles]
+  int* tickets;      // LayerNorm: arrival counter per 128-row panel, zero at launch
   const __half* gamma;
   const __half* beta;
   float eps;
@@ -59,38 +63,33 @@ struct GemmShape {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   static constexpr int kBarBytes = 256;
-  static constexpr int kStatBytes = 2 * kBM * 4;  // LayerNorm: mean and rstd per row of the CTA
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + kStatBytes + 1024;  // + alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kThreads = 192;
   static_assert(BN == 64 || BN == 128 || BN == 256, "UMMA N of the tile");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
-  static_assert((2 * kStages + 4) * 8 + 16 <= kBarBytes, "barrier block too small");
+  static_assert((2 * kStages + 4) * 8 + 16 <= kBarBytes, "barrier block too small");  // + tmem, abort, ticket
 };
 
 struct WorkItem {
   int mt, nt;        // tile coordinates
   int kb0, kb1;      // k-block range [kb0, kb1)
   int slice;         // split-K slice index
-  bool panel_first;  // LayerNorm: first / last N tile of a row panel
-  bool panel_last;
 };
 
 // The j-th work item of the CTA (pair) whose first item index is `first` with `stride` CTAs (pairs)
 // in the grid.  Returns false past the end.  All three roles call this with the same arguments and
 // therefore walk identical sequences.
-//   GEMM:      items are tiles; groups of `group_m` M-tiles are walked N-major so that tiles in
-//              flight together share A rows and B rows in L2 (the reference's CTA remap at
+//   GEMM, LayerNorm: items are tiles; groups of `group_m` M-tiles are walked N-major so that tiles
+//              in flight together share A rows and B rows in L2 (the reference's CTA remap at
 //              cute_gemm_128x128.cu:23-33, restated for a persistent grid).
 //   split-K:   items are (tile, slice), slice fastest; k-blocks are dealt out as evenly as possible.
-//   LayerNorm: a CTA owns whole row panels: item j -> panel first + (j / n_tiles) * stride.
 template <int kMode>
 __device__ __forceinline__ bool work_item(const GemmParams& p, int first, int stride, int j, int num_kb,
                                           WorkItem& w) {
   w.slice = 0;
   w.kb0 = 0;
   w.kb1 = num_kb;
-  w.panel_first = w.panel_last = false;
-  if constexpr (kMode == kModeGemm) {
+  if constexpr (kMode != kModeSplitK) {
     const int t = first + j * stride;
     if (t >= p.m_tiles * p.n_tiles) return false;
     const int per_group = p.group_m * p.n_tiles;
@@ -101,7 +100,7 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, int first, int st
     w.mt = first_m + r % rows;
     w.nt = r / rows;
     return true;
-  } else if constexpr (kMode == kModeSplitK) {
+  } else {
     const int t = first + j * stride;
     if (t >= p.m_tiles * p.n_tiles * p.slices) return false;
     w.slice = t % p.slices;
@@ -110,14 +109,6 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, int first, int st
     w.mt = tile / p.n_tiles;
     w.kb0 = static_cast<int>(static_cast<long long>(num_kb) * w.slice / p.slices);
     w.kb1 = static_cast<int>(static_cast<long long>(num_kb) * (w.slice + 1) / p.slices);
-    return true;
-  } else {
-    const int panel = first + (j / p.n_tiles) * stride;
-    if (panel >= p.m_tiles) return false;
-    w.mt = panel;
-    w.nt = j % p.n_tiles;
-    w.panel_first = w.nt == 0;
-    w.panel_last = w.nt == p.n_tiles - 1;
     return true;
   }
 }
@@ -157,7 +148,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* row_stats = reinterpret_cast<float*>(smem_gen + kStages * S::kStageBytes + S::kBarBytes);
+  volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -266,7 +257,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are this warp's to read
     const uint32_t row_in_tile = quad * 32u + lane;
     const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
-    float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm running statistics of this thread's row
     WorkItem w;
     for (int j = 0; work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
@@ -279,9 +269,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const int grow = row0 + static_cast<int>(row_in_tile);
       const int col0 = w.nt * BN;
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
-      if constexpr (kMode == kModeLayerNorm) {
-        if (w.panel_first) st_n = st_mean = st_m2 = 0.f;
-      }
+      float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm: this row's statistics over this tile
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
@@ -345,16 +333,27 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::mbar_arrive_cluster(lead_empty0 + 8u * acc);
       }
       if constexpr (kMode == kModeLayerNorm) {
-        if (w.panel_last) {
-          // Publish mean / rstd per row, then every epilogue warp normalises whole rows with
-          // lane = column so that the panel is re-read and the output written in 512-byte runs.
-          row_stats[row_in_tile] = st_mean;
-          row_stats[S::kBM + row_in_tile] = rsqrtf(st_m2 / st_n + p.eps);
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // the 4 epilogue warps only
+        // Publish this row's (mean, M2) over the tile, then take the panel's ticket.  The fence before
+        // the barrier orders every epilogue thread's scratch and statistics stores before the ticket.
+        if (grow < p.m) p.row_part[static_cast<size_t>(grow) * p.n_tiles + w.nt] = make_float2(st_mean, st_m2);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the 4 epilogue warps only
+        if (warp == 2 && lane == 0) *ticket_slot = atomicAdd(p.tickets + row0 / S::kBM, 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = (*ticket_slot == p.n_tiles - 1);
+        if (last) {
+          __threadfence();
+          // Whole rows per warp, lane = column group: the panel is re-read and the output written in
+          // 512-byte runs.  Every lane merges the row's per-tile statistics in tile order.
           const int rows_here = min(S::kBM, p.m - row0);
           for (int r = static_cast<int>(quad); r < rows_here; r += 4) {
-            const float mean = row_stats[r];
-            const float rstd = row_stats[S::kBM + r];
+            float n_acc = 0.f, mean = 0.f, m2 = 0.f;
+            const float2* parts = p.row_part + static_cast<size_t>(row0 + r) * p.n_tiles;
+            for (int t = 0; t < p.n_tiles; ++t) {
+              const float2 pt = __ldcg(parts + t);
+              welford_merge(n_acc, mean, m2, static_cast<float>(min(BN, p.n - t * BN)), pt.x, pt.y);
+            }
+            const float rstd = rsqrtf(m2 / n_acc + p.eps);
             const float* srow = p.scratch + static_cast<size_t>(row0 + r) * p.n;
             __half* orow = p.c + static_cast<size_t>(row0 + r) * p.ldc;
             for (int col = static_cast<int>(lane) * 8; col < p.n; col += 256) {
@@ -377,7 +376,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
               *reinterpret_cast<uint4*>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // row_stats is reused by the next panel
         }
       }
     }
