@@ -1,0 +1,374 @@
+#!/usr/bin/env python
+"""Benchmark of the fp16 rc GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (per GPU): C[8192,8192] = A[8192,8192] x B[8192,8192]^T, fp16 in, fp32 accumulate, fp16 out, inputs
+0.1 * normal(0,1) from a fixed seed.  At N GPUs every rank owns an 8192-row block of A and C and a copy of B
+(weak scaling); at N = 8 this is the row-sharded 65536 x 8192 x 8192 problem.  No collective is on the timed
+path (the all-gather of C is optional and reported separately under "extras").
+
+A step is one launch of the default kernel (`cutlass_gemmrc`: 256x256 tiles on CTA pairs).  `value` is
+whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events, max over ranks.  `e2e` is the same
+metric through the host-buffer entry (pinned host A, B -> device -> kernel -> pinned host C) with the copies
+inside the timed region.  One JSON line on stdout (rank 0).
+
+`--impl reference` times the reference's CPU-side statement of the same GEMM (the fp32 CPU loop of oracle/,
+all host threads) on a bounded sample of rows of the same workload; rank 0 only.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "general-nvgpu-testing_b200"))
+sys.path.insert(0, ROOT)
+
+M_PER_GPU, N, K = 8192, 8192, 8192
+SEED = 1234 + 2
+METRIC = "fp16 gemmrc TFLOP/s (M=8192 per GPU, N=K=8192, fp32 accumulate)"
+UNIT = "TFLOP/s"
+# DRAM bytes per launch of the default kernel at 8192^3 from the committed ncu capture
+# (profiles/gemmrc_256x256_pair_8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
+NCU_DRAM_BYTES_PER_LAUNCH = 1.075315e9 + 1.26765e8
+
+REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+           0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting"}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return {"burst": float(d["bf16_tflops"]), "sustained": float(d.get("bf16_tflops_sustained", 0.0)),
+                    "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Polls SM clock and clock-event reasons through NVML while a timed region runs (reads only)."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                for bit, name in REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def physical_index(local_index):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+def cpu_sample(oracle, a_rows, b, seconds_target):
+    """Times the CPU fp32 loop on the first rows of the workload; returns (TFLOP/s, rows used)."""
+    import numpy as np
+    probe = 32
+    t0 = time.perf_counter()
+    oracle.gemmrc(a_rows[:probe], b)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    rows = int(min(a_rows.shape[0], max(probe, (seconds_target / dt) * probe)))
+    rows = max(16, rows // 16 * 16)
+    t0 = time.perf_counter()
+    oracle.gemmrc(a_rows[:rows], b)
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * b.shape[0] * b.shape[1] / dt * 1e-12, rows, dt
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of this path and its CUDA sources cannot be timed on host cores;
+    its CPU-side statement (fp32 loop, oracle/gemmrc_oracle.c) is timed instead, all threads, bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import build_oracle
+    build_oracle.build()
+    import oracle
+    rng = np.random.Generator(np.random.PCG64(SEED))
+    budget = min(2.0, 150.0 / max(args.steps + args.warmup, 1))
+    b = (rng.standard_normal((N, K), dtype=np.float32) * 0.1).astype(np.float16)
+    a = (rng.standard_normal((1024, K), dtype=np.float32) * 0.1).astype(np.float16)
+    tf, rows, dt = cpu_sample(oracle, a, b, budget)
+    for _ in range(max(args.warmup - 1, 0)):
+        oracle.gemmrc(a[:rows], b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.gemmrc(a[:rows], b)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 2.0 * rows * N * K / dt * 1e-12
+    sample = "first %d rows of A x all of B (%d x %d x %d) per step" % (rows, rows, N, K)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 accumulate of f16 (CPU)", "data": "synthetic",
+        "config": {"workload": "fp16 gemmrc 8192x8192x8192 (BASELINE configs[1]), sampled rows", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def extras(beam, torch, a, b, c, peaks):
+    """Side measurements on rank 0 at N = 1 (bounded to a few seconds): cuBLAS on the same inputs, the split-K
+    shapes against the HBM roofline (CUDA-graph batches over rotating input sets larger than L2), and the fused
+    GEMM+LayerNorm."""
+    out = {}
+
+    def ev_time(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    ms = ev_time(lambda: torch.matmul(a, b.t(), out=c), 20)
+    out["cublas_fp32acc_tflops"] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
+    for name, tb in (("128x128", [128, 128]), ("128x256", [128, 256]), ("256x128", [256, 128]),
+                     ("256x256", [256, 256])):
+        ms = ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb), 10)
+        out["tile_%s_tflops" % name] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
+
+    def graph_us(fns):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for f in fns:
+                    f()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) / len(fns) * 1e3)
+        return sorted(ts)[len(ts) // 2]
+
+    for (m, n, k) in ((128, 256, 65536), (64, 64, 131072)):
+        sets = 6  # 6 x (A + B) > 126 MB of L2, walked cyclically: every launch reads from HBM
+        As = [(torch.rand(m, k, device="cuda") * 2 - 1).half() for _ in range(sets)]
+        Bs = [(torch.rand(n, k, device="cuda") * 2 - 1).half() for _ in range(sets)]
+        cc = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        us = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc)) for i in range(24)])
+        bytes_ = 2.0 * (m * k + n * k + m * n)
+        gbs = bytes_ / (us * 1e-6) * 1e-9
+        out["splitk_%dx%dx%d" % (m, n, k)] = {
+            "us": us, "algorithmic_bytes": bytes_, "GBps": gbs, "hbm_peak_GBps": peaks["hbm_gbs"],
+            "frac_of_%s_hbm" % peaks["source"]: gbs / peaks["hbm_gbs"],
+            "cublas_us": graph_us([(lambda i=i: torch.matmul(As[i % sets], Bs[i % sets].t(), out=cc))
+                                   for i in range(24)])}
+        del As, Bs
+    m, n, k = 16384, 4096, 4096
+    x = (torch.randn(m, k, device="cuda") * 0.02).half()
+    w = (torch.randn(n, k, device="cuda") * 0.02).half()
+    g = (1 + 0.1 * torch.randn(n, device="cuda")).half()
+    bt = (0.1 * torch.randn(n, device="cuda")).half()
+    o = torch.empty(m, n, dtype=torch.float16, device="cuda")
+    ms = ev_time(lambda: beam.cutlass_parallel_gemmrc_lnr(x, w, o, g, bt, 1e-5), 10)
+    out["gemm_layernorm_16384x4096x4096"] = {
+        "ms": ms, "tflops": 2.0 * m * n * k / ms * 1e-9,
+        "torch_matmul_plus_layer_norm_ms": ev_time(
+            lambda: torch.nn.functional.layer_norm(torch.matmul(x, w.t()), (n,), g, bt, 1e-5), 10)}
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import beam
+    if not os.path.exists(beam.library_path()):
+        raise SystemExit("libbeam_b200.so is missing; run python general-nvgpu-testing_b200/build.py")
+    peaks = measured_peaks()
+
+    # Rank r owns rows [r*8192, (r+1)*8192) of the global A; B is replicated (same seed everywhere).
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    b = (torch.randn(N, K, device="cuda", generator=gen) * 0.1).half()
+    gen_a = torch.Generator(device="cuda").manual_seed(SEED + 1000 + rank)
+    a = (torch.randn(M_PER_GPU, K, device="cuda", generator=gen_a) * 0.1).half()
+    c = torch.zeros(M_PER_GPU, N, dtype=torch.float16, device="cuda")
+
+    def step():
+        beam.cutlass_gemmrc(a, b, c)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    st, word = beam.device_status()
+    if st != 0:
+        raise SystemExit("device fault word %#x after warm-up" % word)
+
+    # ---- value: inputs resident in HBM (3 x 128 MB > the 126 MB L2, so no flush is needed between steps)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(physical_index(local)) as clk:
+        start.record()
+        for _ in range(args.steps):
+            step()
+        end.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms_total = start.elapsed_time(end)
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    flops_step_all = 2.0 * M_PER_GPU * N * K * world
+    value = flops_step_all / (ms_step * 1e-3) * 1e-12
+    per_gpu = value / world
+
+    # ---- e2e: host buffers through the host entry, copies inside the timed region
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    hc = torch.empty(M_PER_GPU, N, dtype=torch.float16).pin_memory()
+    for _ in range(2):
+        beam.gemmrc_host(ha, hb, hc)
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        beam.gemmrc_host(ha, hb, hc)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([dt], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step_all / (float(t.item()) / e2e_steps) * 1e-12
+    e2e_ok = bool(torch.equal(hc.cuda(), c))
+
+    if rank == 0:
+        burst = ms_total < 500.0  # a short run sits in the burst regime, a long one under the power cap
+        peak = peaks["burst"] if burst or not peaks["sustained"] else peaks["sustained"]
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 in, f32 accumulate, f16 out", "data": "synthetic",
+            "config": {"workload": "fp16 gemmrc M=%d N=%d K=%d (BASELINE configs[1] per GPU; row-sharded "
+                                   "configs[4] at 8 GPUs)" % (M_PER_GPU * world, N, K),
+                       "rows_per_gpu": M_PER_GPU, "kernel": "cutlass_gemmrc: 256x256 tile, cta_group::2, 6-stage TMA "
+                       "ring", "parallelism": "rows of A sharded x%d, B replicated, no collective" % world,
+                       "l2": "A, B, C are 3 x 128 MiB per GPU, larger than the 126 MB L2; no flush between steps"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * (M_PER_GPU * K + N * K) * world,
+                    "d2h_bytes_per_step": 2 * M_PER_GPU * N * world, "steps": e2e_steps, "matches_device_path": e2e_ok,
+                    "timer": "host clock around the blocking call (copies and kernels on internal streams)"},
+            "gpu_launches": args.steps,
+            "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": UNIT, "frac": per_gpu / peak,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "peak_source": "%s cuBLAS bf16 %s of %s" % (peaks["source"], "burst" if burst else "sustained",
+                                                                     "MEASURED_PEAKS.json" if peaks["source"] ==
+                                                                     "measured" else "the profiling recipe"),
+                         "algorithmic_flops_per_launch": 2.0 * M_PER_GPU * N * K,
+                         "frac_of_spec_2250": per_gpu / 2250.0},
+        }
+        if world == 1:
+            from oracle import build_oracle
+            build_oracle.build()
+            import oracle
+            tf, rows, dt = cpu_sample(oracle, ha.numpy(), hb.numpy(), 10.0)
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                                    "sample": "first %d rows of A x all of B (%d x %d x %d), %.1f s" %
+                                              (rows, rows, N, K, dt)}
+            if not args.no_extras:
+                try:
+                    line["extras"] = extras(beam, torch, a, b, c, peaks)
+                except Exception as ex:  # side measurements never take the headline down
+                    line["extras"] = {"error": repr(ex)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the cuBLAS / split-K / LayerNorm side measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

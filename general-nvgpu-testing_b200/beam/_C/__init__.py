@@ -110,12 +110,12 @@ def _check_abc(a, b, c):
     for name, t in (("a", a), ("b", b), ("c", c)):
         if not isinstance(t, torch.Tensor):
             raise TypeError("%s must be a torch.Tensor" % name)
+        if t.dtype != torch.float16:
+            raise TypeError("%s must be float16, got %s" % (name, t.dtype))
         if not t.is_cuda:
             raise ValueError("%s must be a CUDA tensor (there is no CPU path)" % name)
         if not t.is_contiguous():
             raise ValueError("%s must be contiguous" % name)
-        if t.dtype != torch.float16:
-            raise TypeError("%s must be float16, got %s" % (name, t.dtype))
         if t.dim() != 2:
             raise ValueError("%s must be 2-D" % name)
     if not (a.device == b.device == c.device):

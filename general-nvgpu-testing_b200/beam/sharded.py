@@ -1,0 +1,53 @@
+"""Row-sharded rc GEMM over the GPUs of one node (no counterpart in the reference, which is single-GPU:
+python/gemm_test.py:236 only ever calls torch.cuda.set_device(0)).
+
+Rows of C depend only on the same rows of A and on all of B, so the GEMM (and the row-wise LayerNorm
+after it) shards by contiguous blocks of M with no exchange: rank g owns rows [g*M/G, (g+1)*M/G) of A and
+C and a full copy of B.  The only collective is the optional all-gather of C over NCCL/NVLink.
+One process per GPU; torch.distributed carries the plumbing.
+"""
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def row_block(m: int, world: int, rank: int) -> Tuple[int, int]:
+    """[start, stop) of the rows rank `rank` of `world` owns: contiguous, sizes differ by at most one,
+    earlier ranks take the remainder.  Empty blocks are possible when world > m."""
+    if m < 0 or world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad shard request m=%d world=%d rank=%d" % (m, world, rank))
+    base, rem = divmod(m, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def sharded_gemmrc(a_local: torch.Tensor, b: torch.Tensor, c_local: torch.Tensor,
+                   kernel: Optional[Callable] = None) -> None:
+    """c_local = a_local @ b.T on this rank's rows.  `kernel` defaults to beam.cutlass_gemmrc."""
+    if a_local.shape[0] == 0:
+        return
+    if kernel is None:
+        from . import _C
+        kernel = _C.cutlass_gemmrc
+    kernel(a_local, b, c_local)
+
+
+def all_gather_rows(c_local: torch.Tensor, m: int, group=None) -> torch.Tensor:
+    """Assembles the full C [m, N] on every rank from the ranks' row blocks (row_block order).
+    Equal blocks use one all_gather_into_tensor (a single NCCL all-gather over NVLink on GPUs);
+    ragged blocks fall back to per-rank broadcasts."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    n = c_local.shape[1]
+    full = torch.empty((m, n), dtype=c_local.dtype, device=c_local.device)
+    if m % world == 0:
+        dist.all_gather_into_tensor(full, c_local.contiguous(), group=group)
+        return full
+    for r in range(world):
+        s, e = row_block(m, world, r)
+        if e > s:
+            if r == rank:
+                full[s:e].copy_(c_local)
+            dist.broadcast(full[s:e], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
+    return full

@@ -1,0 +1,281 @@
+"""GPU parity tests (pytest -m gpu): the sm_100a kernels, called through the C-ABI library, against the CPU
+oracle, the golden vectors and size-independent properties.
+
+Tolerance: the reference accepts rtol = atol = 2e-2 against torch.matmul (python/gemm_test.py:46); the bar here
+is tighter: max |got - ref| / max(|ref|, 1e-2 * rms(ref)) <= 1e-2 for fp16 outputs (oracle.REL_TOL), which a
+correctly rounded result meets at about 5e-4.  Split-K must in addition be bitwise reproducible.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gemmrc_golden.npz")
+
+
+def _inputs(m, n, k, dist, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    if dist == "uniform":
+        a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+        b = rng.uniform(-1, 1, (n, k)).astype(np.float16)
+    else:
+        a = (rng.standard_normal((m, k), dtype=np.float32) * dist).astype(np.float16)
+        b = (rng.standard_normal((n, k), dtype=np.float32) * dist).astype(np.float16)
+    return a, b
+
+
+def _dev(x):
+    return torch.from_numpy(x).cuda()
+
+
+def _healthy(beam):
+    st, word = beam.device_status()
+    assert (st, word) == (0, 0), "device fault word %#x" % word
+
+
+@pytest.fixture(scope="module")
+def beam(built_library):
+    import beam as beam_pkg
+    assert os.path.exists(beam_pkg.library_path())
+    return beam_pkg
+
+
+REGISTRY = ["custom_gemmrc_128x128", "custom_gemmrc_128x256", "cutlass_gemmrc"]
+
+
+@pytest.mark.parametrize("name", REGISTRY)
+def test_config1_plumbing_512_cubed(beam, oracle_mod, name):
+    """BASELINE config 1: M=N=K=512, uniform [-1,1], checked against the fp32 CPU loop."""
+    a, b = _inputs(512, 512, 512, "uniform", 1234 + 1)
+    want = oracle_mod.gemmrc(a, b)
+    c = torch.zeros(512, 512, dtype=torch.float16, device="cuda")
+    getattr(beam, name)(_dev(a), _dev(b), c)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    assert oracle_mod.max_abs_over_max(c.cpu().numpy(), want) <= 2e-3
+
+
+@pytest.mark.parametrize("tb", [[128, 128], [128, 256], [256, 128], [256, 256]])
+def test_spec_tile_families(beam, oracle_mod, tb):
+    a, b = _inputs(768, 512, 320, "uniform", 21)
+    want = oracle_mod.gemmrc(a, b)
+    c = torch.zeros(768, 512, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc_spec(a=_dev(a), b=_dev(b), c=c, shape_threadblock=tb, shape_warp=[64, 64])
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+
+
+@pytest.mark.parametrize("case", ["tiny", "ragged", "tile", "wide", "deepk"])
+def test_golden_vectors(beam, oracle_mod, case):
+    g = np.load(GOLDEN)
+    a, b, want = g[case + "_a"], g[case + "_b"], g[case + "_c"]
+    for name in REGISTRY:
+        c = torch.full(want.shape, 7.0, dtype=torch.float16, device="cuda")
+        getattr(beam, name)(_dev(a), _dev(b), c)
+        torch.cuda.synchronize()
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL, name
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), g[case + "_c64"]) <= oracle_mod.REL_TOL, name
+    _healthy(beam)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (8, 8, 8), (127, 136, 72), (129, 264, 200), (300, 1000, 1096),
+                                    (257, 520, 64), (1000, 24, 4104)])
+@pytest.mark.parametrize("tile_n,cta_pair", [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2)])
+def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
+    """Edge tiles in M, N and K: out-of-range parts are zero-filled on load and masked on store, and nothing
+    outside C[M,N] is written."""
+    a, b = _inputs(m, n, k, "uniform", m * 31 + n * 7 + k)
+    want = oracle_mod.gemmrc(a, b)
+    guard = torch.full((m + 2, n), 3.0, dtype=torch.float16, device="cuda")
+    c = guard[1:m + 1]
+    beam.gemmrc(_dev(a), _dev(b), c, tile_n=tile_n, cta_pair=cta_pair)
+    torch.cuda.synchronize()
+    assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    assert (guard[0] == 3.0).all() and (guard[m + 1] == 3.0).all()
+    _healthy(beam)
+
+
+def test_zero_and_identity_inputs(beam):
+    n = 384
+    eye = torch.eye(n, dtype=torch.float16, device="cuda")
+    b = ((torch.arange(n * n, device="cuda").reshape(n, n) % 2048) - 1024).half()
+    c = torch.empty(n, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc(eye, b, c)  # I * B^T = B^T exactly
+    assert torch.equal(c, b.t())
+    beam.cutlass_gemmrc(torch.zeros_like(eye), b, c)
+    assert (c == 0).all()
+
+
+def test_linearity_property(beam):
+    """(2A) B^T = 2 (A B^T) bit for bit (scaling by two is exact in fp16 and fp32 away from overflow)."""
+    a, b = _inputs(640, 512, 1024, 0.1, 77)
+    da, db = _dev(a), _dev(b)
+    c1 = torch.empty(640, 512, dtype=torch.float16, device="cuda")
+    c2 = torch.empty_like(c1)
+    beam.cutlass_gemmrc(da, db, c1)
+    beam.cutlass_gemmrc(da * 2, db, c2)
+    assert torch.equal(c2, c1 * 2)
+
+
+def test_config2_8192_cubed(beam, oracle_mod):
+    """BASELINE config 2 at full size: every tile family against cuBLAS (fp32 accumulate) on all elements,
+    and 24 sampled rows against the fp64 CPU oracle."""
+    m = n = k = 8192
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 2)
+    a = (torch.randn(m, k, device="cuda", generator=gen) * 0.1).half()
+    b = (torch.randn(n, k, device="cuda", generator=gen) * 0.1).half()
+    ref = torch.matmul(a, b.t())
+    rows = np.linspace(0, m - 1, 24).astype(np.int32)
+    truth = oracle_mod.gemmrc_rows_f64(a.cpu().numpy(), b.cpu().numpy(), rows)
+    rms = float(np.sqrt(np.mean(truth * truth)))
+    for tb in ([128, 128], [128, 256], [256, 128], [256, 256]):
+        c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb)
+        torch.cuda.synchronize()
+        _healthy(beam)
+        got_rows = c[torch.from_numpy(rows).long().cuda()].cpu().numpy()
+        assert oracle_mod.floored_max_rel(got_rows, truth, rms) <= oracle_mod.REL_TOL, tb
+        d = (c.float() - ref.float()).abs()
+        den = torch.clamp(ref.float().abs(), min=1e-2 * rms)
+        assert float((d / den).max()) <= oracle_mod.REL_TOL, tb
+
+
+SPLITK_CASES = [
+    # m, n, k, tile_n, slices
+    (128, 256, 65536, 128, 0), (128, 256, 65536, 128, 4), (128, 256, 65536, 128, 64), (128, 256, 65536, 256, 32),
+    (128, 256, 65536, 64, 16), (64, 64, 131072, 64, 0), (64, 64, 131072, 64, 8), (64, 64, 131072, 64, 64),
+    (40, 72, 1096, 64, 3), (200, 136, 2048, 128, 5),
+]
+
+
+@pytest.mark.parametrize("m,n,k,tile_n,slices", SPLITK_CASES)
+def test_config3_splitk(beam, oracle_mod, m, n, k, tile_n, slices):
+    """BASELINE config 3 (both shapes) and ragged cases: parity with the fp32 CPU loop and with the slice-ordered
+    restatement, and bitwise identical results on a second run."""
+    a, b = _inputs(m, n, k, "uniform", 1234 + 3 + slices)
+    want = oracle_mod.gemmrc(a, b)
+    da, db = _dev(a), _dev(b)
+    c = torch.full((m, n), 5.0, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc_splitk_spec(da, db, c, shape_threadblock=[128, tile_n], split_k_slices=slices)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    got = c.cpu().numpy()
+    assert oracle_mod.floored_max_rel(got, want) <= oracle_mod.REL_TOL
+    if slices > 0:
+        assert oracle_mod.floored_max_rel(got, oracle_mod.gemmrc_splitk(a, b, slices)) <= oracle_mod.REL_TOL
+    c2 = torch.zeros_like(c)
+    beam.cutlass_gemmrc_splitk_spec(da, db, c2, shape_threadblock=[128, tile_n], split_k_slices=slices)
+    assert torch.equal(c, c2), "split-K must be bitwise reproducible"
+
+
+def test_splitk_default_entry(beam, oracle_mod):
+    a, b = _inputs(128, 256, 8192, "uniform", 99)
+    want = oracle_mod.gemmrc(a, b)
+    c = torch.zeros(128, 256, dtype=torch.float16, device="cuda")
+    for s in (0, 7, 100000):  # heuristic, explicit, out of range (falls back to the heuristic)
+        c.zero_()
+        beam.cutlass_gemmrc_splitk(a=_dev(a), b=_dev(b), c=c, split_k_slices=s)
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (300, 1000, 264), (512, 4096, 512), (96, 264, 320)])
+def test_config4_layernorm_small(beam, oracle_mod, m, n, k):
+    rng = np.random.Generator(np.random.PCG64(1234 + 4))
+    x = (rng.standard_normal((m, k)) * 0.02).astype(np.float16)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float16)
+    gamma = (1 + 0.1 * rng.standard_normal(n)).astype(np.float16)
+    beta = (0.1 * rng.standard_normal(n)).astype(np.float16)
+    want = oracle_mod.gemm_layernorm(x, w, gamma, beta, 1e-5)
+    out = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_parallel_gemmrc_lnr(_dev(x), _dev(w), out, _dev(gamma), _dev(beta), 1e-5)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert oracle_mod.floored_max_rel(out.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    out2 = torch.zeros_like(out)
+    beam.cutlass_parallel_gemmrc_lnr(_dev(x), _dev(w), out2, _dev(gamma), _dev(beta), 1e-5)
+    assert torch.equal(out, out2)
+
+
+def test_golden_layernorm(beam, oracle_mod):
+    g = np.load(GOLDEN)
+    for case in ("ragged", "tile", "wide"):
+        a, b = g[case + "_a"], g[case + "_b"]
+        out = torch.zeros(a.shape[0], b.shape[0], dtype=torch.float16, device="cuda")
+        beam.cutlass_parallel_gemmrc_lnr(_dev(a), _dev(b), out, _dev(g[case + "_gamma"]), _dev(g[case + "_beta"]),
+                                         1e-5)
+        assert oracle_mod.floored_max_rel(out.cpu().numpy(), g[case + "_ln64"]) <= oracle_mod.REL_TOL, case
+
+
+def test_config4_layernorm_full_size(beam, oracle_mod):
+    """BASELINE config 4: X[16384,4096] x W[4096,4096]^T + LayerNorm; 16 sampled rows against the fp64 oracle,
+    and the row statistics of the whole output: mean of (out - beta) / gamma ~ 0 and variance ~ 1."""
+    m, n, k = 16384, 4096, 4096
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 4)
+    x = (torch.randn(m, k, device="cuda", generator=gen) * 0.02).half()
+    w = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).half()
+    gamma = (1 + 0.1 * torch.randn(n, device="cuda", generator=gen)).half()
+    beta = (0.1 * torch.randn(n, device="cuda", generator=gen)).half()
+    out = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_parallel_gemmrc_lnr(x, w, out, gamma, beta, 1e-5)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    rows = np.linspace(0, m - 1, 16).astype(np.int32)
+    truth = oracle_mod.gemm_layernorm_rows_f64(x.cpu().numpy(), w.cpu().numpy(), gamma.cpu().numpy(),
+                                               beta.cpu().numpy(), rows, 1e-5)
+    got = out[torch.from_numpy(rows).long().cuda()].cpu().numpy()
+    assert oracle_mod.floored_max_rel(got, truth) <= oracle_mod.REL_TOL
+    z = (out.float() - beta.float()) / gamma.float()
+    assert float(z.mean(dim=1).abs().max()) < 5e-3
+    assert float((z.var(dim=1, unbiased=False) - 1).abs().max()) < 2e-2
+
+
+def test_error_paths_on_device(beam):
+    a = torch.zeros(64, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        beam.cutlass_gemmrc(a, a[:, :32].contiguous(), a)          # K mismatch
+    with pytest.raises(ValueError):
+        beam.cutlass_gemmrc(a, a, torch.zeros(64, 32, dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        beam.cutlass_gemmrc(a.t(), a, a)                            # not contiguous
+    with pytest.raises(TypeError):
+        beam.cutlass_gemmrc(a.float(), a, a)
+    with pytest.raises(ValueError):
+        beam.cutlass_gemmrc_spec(a, a, a, shape_threadblock=[64, 64])
+    a60 = torch.zeros(64, 60, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        beam.cutlass_gemmrc(a60, a60, a)                            # K % 8 != 0
+    lib = ctypes.CDLL(beam.library_path())
+    sk = lib.beam_cutlass_gemmrc_splitk
+    vp, i = ctypes.c_void_p, ctypes.c_int
+    sk.argtypes = [vp, vp, vp, i, i, i, i, vp, ctypes.c_size_t, vp]
+    ws = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    big = torch.zeros(64, 4096, dtype=torch.float16, device="cuda")
+    assert sk(big.data_ptr(), big.data_ptr(), a.data_ptr(), 64, 64, 4096, 8, ws.data_ptr(), 1024, None) == 4
+    assert sk(big.data_ptr(), big.data_ptr(), a.data_ptr(), 64, 64, 4096, 8, None, 0, None) == 4
+    _healthy(beam)
+
+
+def test_host_buffer_entry(beam, oracle_mod):
+    a, b = _inputs(1000, 520, 264, 0.1, 5)
+    want = oracle_mod.gemmrc(a, b)
+    c = torch.zeros(1000, 520, dtype=torch.float16)
+    beam.gemmrc_host(torch.from_numpy(a), torch.from_numpy(b), c)
+    assert oracle_mod.floored_max_rel(c.numpy(), want) <= oracle_mod.REL_TOL
+    pa, pb = torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()
+    pc = torch.zeros(1000, 520, dtype=torch.float16).pin_memory()
+    beam.gemmrc_host(pa, pb, pc)
+    assert torch.equal(pc, c)
+
+
+def test_tuner_picks_a_kernel(beam):
+    tuner = beam.OperatorTuner()
+    tuner.gemm_ops = tuner.gemm_ops[:5] + tuner.gemm_ops[5:8]   # a short list keeps the test fast
+    op, tflops = tuner.tune([2048, 2048, 2048])
+    assert op is not None and 1.0 < tflops < 2500.0
+    assert tuner.tune([2048, 2048, 2048]) == (op, tflops)
