@@ -111,7 +111,7 @@ def physical_index(local_index):
 def cpu_sample(oracle, a_rows, b, seconds_target):
     """Times the CPU fp32 loop on the first rows of the workload; returns (TFLOP/s, rows used)."""
     import numpy as np
-    probe = 32
+    probe = min(256, a_rows.shape[0])  # large enough to amortise the one-off widening of B
     t0 = time.perf_counter()
     oracle.gemmrc(a_rows[:probe], b)
     dt = max(time.perf_counter() - t0, 1e-4)
