@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbeam_b200.so")
-SOURCES = ["gemmrc_launch.cu", "host_entry.cu", "host_common.cc", "beam_api.cc"]
+SOURCES = ["gemmrc_launch.cu", "splitk_static.cu", "host_entry.cu", "host_common.cc", "beam_api.cc"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

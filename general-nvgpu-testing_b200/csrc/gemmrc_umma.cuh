@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
 // ascending) for 4 columns, then the 8 group sums are added in ascending g.  The association order
 // depends only on the slice count, never on timing, so results are bitwise reproducible.
 constexpr int kReduceGroups = 8;
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial,
+static __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial,
                                                             __half* __restrict__ c, int m, int n, int slices) {
   asm volatile("griddepcontrol.wait;" ::: "memory");  // partials of the producing kernel are complete
   __shared__ float4 sums[kReduceGroups][32];

@@ -126,6 +126,24 @@ BEAM_API int beam_cutlass_gemmrc_splitk_spec(const void* A, const void* B, void*
                                     int tb_n, int warp_m, int warp_n, int split_k_slices, void* workspace,
                                     size_t workspace_bytes, void* stream);
 
+/* Split-K for callers that must not allocate (no counterpart in the reference, whose split-K grows a
+ * hidden cudaMalloc'd buffer on demand).  Same arithmetic and kernels as beam_cutlass_gemmrc_splitk, but
+ * the fp32 partials live in a 16 MiB array that is part of the library's device image, so the caller passes
+ * only inputs and outputs: for host threads in latency-critical loops (cudaMalloc/cudaFree serialise on the
+ * driver's allocator and cudaFree synchronises the device), for processes that gave all device memory to
+ * another allocator at start-up, and for runtimes that forbid allocation after initialisation.
+ *   - limit: slices * M * N * 4 bytes <= 16 MiB, otherwise BEAM_ERR_WORKSPACE (use the workspace entry);
+ *     the array occupies 16 MiB on every GPU that loads the library until the process exits;
+ *   - the first call on a device does a one-time set-up (symbol address, kernel attributes): make it
+ *     before any stream capture starts on that device;
+ *   - calls no cudaMalloc / cudaFree / allocating routine and does not touch the library's per-device
+ *     context, so beam_device_status() does not see its kernels: pass `device_fault_word` (a zeroed
+ *     4-byte device int of your own, or NULL) to receive a DeviceFault code if a bounded wait expires;
+ *   - all calls on a device share the array, which keeps the previous call's contents (nothing in it needs
+ *     to start at zero; each call overwrites what it reads).  Calls that overlap on the GPU race. */
+BEAM_API int beam_gemmrc_splitk_noalloc(const void* A, const void* B, void* C, int m, int n, int k,
+                                        int split_k_slices, int* device_fault_word, void* stream);
+
 /* ---- fused GEMM + LayerNorm --------------------------------------------------------------------- */
 
 /* Scratch bytes for beam_gemmrc_layernorm: fp32 row statistics exchanged between the N-tiles. */

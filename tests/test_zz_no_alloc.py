@@ -1,0 +1,73 @@
+"""GPU test of beam_gemmrc_splitk_noalloc, the split-K entry point for callers that are not allowed to
+allocate device memory (serving loops that cannot afford the allocator's device-wide synchronisation,
+processes whose device memory is already owned by another allocator, runtimes with a no-allocation-after-
+init rule).  It is called through the C ABI with inputs and outputs only; its partial tiles live in a fixed
+16 MiB array inside the library.  The test checks it against the ordinary workspace entry point on two
+calls in a row (the second call reuses the array with the first call's leftovers in it), on a second shape,
+and checks that a problem too large for the fixed array is refused.
+
+This file sorts last on purpose: a run that stops at the first failure has then already run every other test.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bind(lib_path):
+    L = ctypes.CDLL(lib_path)
+    vp, i, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    L.beam_gemmrc_splitk_noalloc.argtypes = [vp, vp, vp, i, i, i, i, vp, vp]
+    L.beam_cutlass_gemmrc_splitk.argtypes = [vp, vp, vp, i, i, i, i, vp, sz, vp]
+    L.beam_gemmrc_splitk_workspace_bytes.restype = sz
+    L.beam_gemmrc_splitk_workspace_bytes.argtypes = [i, i, i, i, i]
+    return L
+
+
+def _case(m, n, k, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).half()
+    b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
+    return a, b
+
+
+def test_noalloc_matches_workspace_entry_twice_in_a_row(built_library, oracle_mod):
+    L = _bind(built_library)
+    torch.cuda.set_device(0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fault = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for (m, n, k, slices, seed) in ((128, 256, 8192, 16, 1), (128, 256, 8192, 16, 2), (64, 64, 16384, 0, 3)):
+        a, b = _case(m, n, k, seed)
+        want = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, 0, slices)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        st = L.beam_cutlass_gemmrc_splitk(a.data_ptr(), b.data_ptr(), want.data_ptr(), m, n, k, slices,
+                                          ws.data_ptr(), ws.numel(), stream)
+        assert st == 0
+        got = torch.full((m, n), 9.0, dtype=torch.float16, device="cuda")
+        st = L.beam_gemmrc_splitk_noalloc(a.data_ptr(), b.data_ptr(), got.data_ptr(), m, n, k, slices,
+                                          fault.data_ptr(), stream)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert int(fault.item()) == 0
+        # same kernels, same reduction order: equal within the parity tolerance (in fact bit for bit)
+        assert oracle_mod.floored_max_rel(got.cpu().numpy(), want.cpu().numpy()) <= oracle_mod.REL_TOL
+        ref = oracle_mod.gemmrc(a.cpu().numpy(), b.cpu().numpy())
+        assert oracle_mod.floored_max_rel(got.cpu().numpy(), ref) <= oracle_mod.REL_TOL
+
+
+def test_noalloc_refuses_what_does_not_fit(built_library):
+    L = _bind(built_library)
+    torch.cuda.set_device(0)
+    m, n, k, slices = 512, 1024, 4096, 16          # 16 * 512 * 1024 * 4 bytes = 32 MiB > 16 MiB
+    a, b = _case(m, n, k, 4)
+    c = torch.full((m, n), 2.0, dtype=torch.float16, device="cuda")
+    st = L.beam_gemmrc_splitk_noalloc(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, slices, None, None)
+    assert st == 4                                   # BEAM_ERR_WORKSPACE
+    torch.cuda.synchronize()
+    assert (c == 2.0).all()                          # nothing ran
+    assert L.beam_gemmrc_splitk_noalloc(None, b.data_ptr(), c.data_ptr(), m, n, k, slices, None, None) == 1
