@@ -8,6 +8,14 @@
 
 namespace beam {
 
+#ifdef BEAM_TRACE
+// Diagnostic builds only (never part of the shipped library): where kernels drop their time stamps.
+static unsigned long long* g_trace_buffer = nullptr;
+extern "C" __attribute__((visibility("default"))) void beam_debug_set_trace(unsigned long long* device_buffer) {
+  g_trace_buffer = device_buffer;
+}
+#endif
+
 namespace {
 
 struct ExtraArgs {
@@ -18,6 +26,7 @@ struct ExtraArgs {
   int slices = 1;
   float2* row_part = nullptr;
   int* tickets = nullptr;
+  int* ln_queue = nullptr;
 };
 
 template <int BN, int kStages, int kCta, int kMode>
@@ -66,6 +75,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.scratch = ex.scratch;
   p.row_part = ex.row_part;
   p.tickets = ex.tickets;
+  p.ln_queue = ex.ln_queue;
   p.gamma = ex.gamma;
   p.beta = ex.beta;
   p.eps = ex.eps;
@@ -79,6 +89,9 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 8 : 16);
   p.slices = ex.slices;
   p.status = ctx->status_word;
+#ifdef BEAM_TRACE
+  p.trace = g_trace_buffer;
+#endif
 
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
   int clusters = resident;
@@ -233,21 +246,23 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
 }
 
 // ------------------------------------------------------------------------ GEMM + LayerNorm
-// Workspace layout: [fp32 panel M x N][(mean, M2) per row per 256-wide N tile][ticket per 128 rows].
+// Workspace layout: [fp32 panel M x N][(mean, M2) per row per 256-wide N tile][ticket per 128 rows]
+// [queue: 16 control ints + one int per 128-row panel].  Tickets and queue are zeroed before each launch.
 namespace {
 constexpr int kLnTileN = 256;
 struct LnLayout {
-  size_t panel_bytes, part_off, part_bytes, ticket_off, ticket_bytes, total;
+  size_t panel_bytes, part_off, part_bytes, ticket_off, ticket_bytes, queue_off, total;  // ticket_bytes covers the queue too
 };
 LnLayout ln_layout(int m, int n) {
   LnLayout l;
   const size_t n_tiles = static_cast<size_t>((n + kLnTileN - 1) / kLnTileN);
-  const size_t panels = static_cast<size_t>((m + 127) / 128);
+  const size_t panels = 2 * static_cast<size_t>((m + 255) / 256);  // both CTAs of every 256-row pair tile
   l.panel_bytes = (static_cast<size_t>(m) * n * sizeof(float) + 255) / 256 * 256;
   l.part_off = l.panel_bytes;
   l.part_bytes = (static_cast<size_t>(m) * n_tiles * sizeof(float2) + 255) / 256 * 256;
   l.ticket_off = l.part_off + l.part_bytes;
-  l.ticket_bytes = (panels * sizeof(int) + 255) / 256 * 256;
+  l.ticket_bytes = (panels * sizeof(int) + 255) / 256 * 256 + ((16 + panels) * sizeof(int) + 255) / 256 * 256;
+  l.queue_off = l.ticket_off + (panels * sizeof(int) + 255) / 256 * 256;
   l.total = l.ticket_off + l.ticket_bytes;
   return l;
 }
@@ -275,6 +290,7 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   ex.scratch = reinterpret_cast<float*>(ws);
   ex.row_part = reinterpret_cast<float2*>(ws + l.part_off);
   ex.tickets = reinterpret_cast<int*>(ws + l.ticket_off);
+  ex.ln_queue = reinterpret_cast<int*>(ws + l.queue_off);
   ex.gamma = static_cast<const __half*>(gamma);
   ex.beta = static_cast<const __half*>(beta);
   ex.eps = eps;

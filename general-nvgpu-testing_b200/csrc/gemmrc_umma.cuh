@@ -24,8 +24,10 @@
 //   kModeLayerNorm  tiles are walked in GEMM order (so A and B stay L2-resident).  Each tile's epilogue
 //                   parks its fp32 values in a scratch panel, writes one (mean, M2) pair per row for
 //                   its N range, and takes a ticket for its 128-row panel.  The CTA that draws the last
-//                   ticket of a panel merges the per-tile statistics in tile order, re-reads the panel
-//                   (still in L2), normalises, applies gamma/beta and stores fp16.  Nobody waits.
+//                   ticket of a panel publishes the panel on a device-wide queue; after every tile each
+//                   CTA claims a few 8-row chunks of published panels and normalises them (statistics
+//                   merged in tile order, panel re-read from L2, gamma/beta applied, fp16 stored), so the
+//                   second pass is spread over all SMs and hidden under the main loops.
 #pragma once
 
 #include "umma_common.cuh"
@@ -41,6 +43,7 @@ struct GemmParams {
   float* scratch;    // split-K: partials [slices][M][N]; LayerNorm: fp32 panel store [M][N]
   float2* row_part;  // LayerNorm: (mean, M2) of every row over each N tile, [M][n_tiles]
   int* tickets;      // LayerNorm: arrival counter per 128-row panel, zero at launch
+  int* ln_queue;     // LayerNorm: [0] panels published, [1] chunks claimed, [16 + i] i-th published panel + 1
   const __half* gamma;
   const __half* beta;
   float eps;
@@ -51,7 +54,21 @@ struct GemmParams {
   int group_m;  // M-tiles per rasterisation group (GEMM mode)
   int slices;   // split-K slices (1 otherwise)
   int* status;  // device fault word
+#ifdef BEAM_TRACE
+  unsigned long long* trace;  // diagnostic builds only: 8 globaltimer stamps per CTA
+#endif
 };
+
+#ifdef BEAM_TRACE
+#define BEAM_STAMP(slot)                                                                      \
+  do {                                                                                        \
+    if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * 8 + (slot)] = ptx::globaltimer_ns(); \
+  } while (0)
+#else
+#define BEAM_STAMP(slot) \
+  do {                   \
+  } while (0)
+#endif
 
 template <int BN, int kStages, int kCta>
 struct GemmShape {
@@ -67,7 +84,7 @@ struct GemmShape {
   static constexpr int kThreads = 192;
   static_assert(BN == 64 || BN == 128 || BN == 256, "UMMA N of the tile");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
-  static_assert((2 * kStages + 4) * 8 + 16 <= kBarBytes, "barrier block too small");  // + tmem, abort, ticket
+  static_assert((2 * kStages + 4) * 8 + 32 <= kBarBytes, "barrier block too small");  // + tmem, abort, 4 slots
 };
 
 struct WorkItem {
@@ -123,6 +140,141 @@ __device__ __forceinline__ void welford_merge(float& n, float& mean, float& m2, 
   n = nn;
 }
 
+// ------------------------------------------------------------------ LayerNorm second pass
+constexpr int kLnChunkRows = 8;                        // rows per claimed chunk: two per epilogue warp
+constexpr int kLnChunksPerPanel = 128 / kLnChunkRows;  // a panel is 128 rows
+constexpr int kLnQueueItems = 16;                      // int offset of the published-panel list
+
+__device__ __forceinline__ int ld_volatile_i32(const int* ptr) {
+  return *reinterpret_cast<const volatile int*>(ptr);
+}
+
+// One warp normalises one complete output row: merges the row's per-tile (mean, M2) in tile order
+// (lanes fetch 32 tiles at a time, then every lane replays the same merge sequence from shuffles),
+// then streams the parked fp32 row with 16 independent 16-byte loads in flight per lane.
+template <int BN>
+__device__ __forceinline__ void ln_normalise_row(const GemmParams& p, int row, uint32_t lane) {
+  float n_acc = 0.f, mean = 0.f, m2 = 0.f;
+  const float2* parts = p.row_part + static_cast<size_t>(row) * p.n_tiles;
+  for (int t0 = 0; t0 < p.n_tiles; t0 += 32) {
+    const int t = t0 + static_cast<int>(lane);
+    float2 mine = make_float2(0.f, 0.f);
+    if (t < p.n_tiles) mine = __ldcg(parts + t);
+    const int cnt = min(32, p.n_tiles - t0);
+    for (int i = 0; i < cnt; ++i) {
+      const float mb = __shfl_sync(0xffffffffu, mine.x, i);
+      const float m2b = __shfl_sync(0xffffffffu, mine.y, i);
+      welford_merge(n_acc, mean, m2, static_cast<float>(min(BN, p.n - (t0 + i) * BN)), mb, m2b);
+    }
+  }
+  const float rstd = rsqrtf(m2 / n_acc + p.eps);
+  const float* srow = p.scratch + static_cast<size_t>(row) * p.n;
+  __half* orow = p.c + static_cast<size_t>(row) * p.ldc;
+  constexpr int kUnits = 8;  // 8 columns per unit and lane: 2048 columns per sweep of the warp
+  for (int base = 0; base < p.n; base += 256 * kUnits) {
+    float4 x0[kUnits], x1[kUnits];
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) {
+      const int col = base + u * 256 + static_cast<int>(lane) * 8;
+      x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col < p.n) {
+        x0[u] = __ldcg(reinterpret_cast<const float4*>(srow + col));
+        x1[u] = __ldcg(reinterpret_cast<const float4*>(srow + col + 4));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) {
+      const int col = base + u * 256 + static_cast<int>(lane) * 8;
+      if (col < p.n) {
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(p.gamma + col));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.beta + col));
+        const __half2* g2 = reinterpret_cast<const __half2*>(&g);
+        const __half2* b2 = reinterpret_cast<const __half2*>(&b);
+        const float xs[8] = {x0[u].x, x0[u].y, x0[u].z, x0[u].w, x1[u].x, x1[u].y, x1[u].z, x1[u].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 gf = __half22float2(g2[q]);
+          const float2 bf = __half22float2(b2[q]);
+          o[q] = ptx::pack_half2((xs[2 * q] - mean) * rstd * gf.x + bf.x, (xs[2 * q + 1] - mean) * rstd * gf.y + bf.y);
+        }
+        *reinterpret_cast<uint4*>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
+// One visit of the four epilogue warps to the device-wide queue of panels whose statistics are complete.
+// The deciding thread (decider == true for exactly one of the 128 threads) claims up to two chunks with
+// atomicAdd on the claim counter and posts them in `slots`; all four warps then normalise them, two rows
+// per warp and chunk.  A claim can run ahead of publication (the counter is bumped before the panel it
+// falls into is published): such a chunk is kept in `pending` and retried at the next visit.
+// slots: [0] chunks to do now, [1], [2] their ids, [3] 1 = every chunk of the problem has been claimed and
+// this CTA holds no pending claim.
+// deadline_ns != 0 (the drain after the last tile): past it, or once the CTA has aborted, the decider
+// reports a fault and tells everyone to leave.
+template <int BN>
+__device__ __forceinline__ bool ln_visit(const GemmParams& p, volatile int* slots, int& pending, bool decider,
+                                         uint32_t quad, uint32_t lane, volatile int* cta_abort,
+                                         uint64_t deadline_ns) {
+  int* q = p.ln_queue;
+  const int panels = (p.m + 127) / 128;
+  const int total_chunks = panels * kLnChunksPerPanel;
+  if (decider) {
+    auto ready = [&](int c) {
+      const int slot = c / kLnChunksPerPanel;
+      return slot < ld_volatile_i32(q) && ld_volatile_i32(q + kLnQueueItems + slot) != 0;
+    };
+    int count = 0;
+    if (pending >= 0 && ready(pending)) {
+      slots[1 + count++] = pending;
+      pending = -1;
+    }
+    bool exhausted = false;
+    while (count < 2 && pending < 0) {
+      const int head = ld_volatile_i32(q + 1);
+      if (head >= total_chunks) {
+        exhausted = true;
+        break;
+      }
+      if (head >= ld_volatile_i32(q) * kLnChunksPerPanel) break;  // nothing published beyond the claims
+      const int c = atomicAdd(q + 1, 1);
+      if (c >= total_chunks) {
+        exhausted = true;
+        break;
+      }
+      if (ready(c))
+        slots[1 + count++] = c;
+      else
+        pending = c;
+    }
+    slots[0] = count;
+    slots[3] = (exhausted && pending < 0) ? 1 : 0;
+    if (deadline_ns != 0 && count == 0 && slots[3] == 0) {
+      if (!*cta_abort && ptx::globaltimer_ns() > deadline_ns) {
+        *cta_abort = 1;
+        if (p.status) atomicCAS(p.status, 0, static_cast<int>(kFaultReduceWait));
+      }
+      if (*cta_abort) slots[3] = 1;
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const int count = slots[0];
+  const bool all_claimed = slots[3] != 0;
+  if (count > 0) {
+    __threadfence();  // acquire side of the publication: panel data and statistics are visible below
+    for (int i = 0; i < count; ++i) {
+      const int c = slots[1 + i];
+      const int panel = ld_volatile_i32(q + kLnQueueItems + c / kLnChunksPerPanel) - 1;
+      const int row0 = panel * 128 + (c % kLnChunksPerPanel) * kLnChunkRows + static_cast<int>(quad) * 2;
+      if (row0 < p.m) ln_normalise_row<BN>(p, row0, lane);
+      if (row0 + 1 < p.m) ln_normalise_row<BN>(p, row0 + 1, lane);
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // slots may be rewritten by the next visit
+  return all_claimed && count == 0;
+}
+
 template <int BN, int kStages, int kCta, int kMode>
 __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmShape<BN, kStages, kCta>;
@@ -130,6 +282,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) BEAM_STAMP(0);
   const uint32_t cta_rank = (kCta == 2) ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
   const int stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -148,7 +301,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* ln_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);  // 4 ints, LayerNorm visits
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -173,6 +326,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   if constexpr (kCta == 2) ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) BEAM_STAMP(1);
   if constexpr (kMode == kModeSplitK) {
     // Let the reduction kernel's blocks become resident early; they block until this grid is done.
     if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -200,6 +354,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
             ptx::tma_load_2d(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a);
             ptx::tma_load_2d(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b);
+            if (it == 0) BEAM_STAMP(2);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
@@ -231,6 +386,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             break;
           }
           ptx::tc_fence_after();
+          if (it == 0) BEAM_STAMP(3);
           const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s));
           const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s));
 #pragma unroll
@@ -245,6 +401,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
         if (alive) {
+          BEAM_STAMP(4);
           if constexpr (kCta == 1)
             ptx::umma_commit<1>(tmem_full_bar(acc));
           else
@@ -257,6 +414,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are this warp's to read
     const uint32_t row_in_tile = quad * 32u + lane;
     const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    const bool ln_decider = (warp == 2 && lane == 0);  // LayerNorm: the one thread that talks to the queue
+    int ln_pending = -1;                               // LayerNorm: a chunk claimed ahead of its publication
     WorkItem w;
     for (int j = 0; work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
@@ -265,6 +424,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const bool ready = bounded_wait(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait);
       if (!__all_sync(0xffffffffu, ready)) break;
       ptx::tc_fence_after();
+      if (threadIdx.x == 64) BEAM_STAMP(5);
       const int row0 = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;  // first row of this CTA
       const int grow = row0 + static_cast<int>(row_in_tile);
       const int col0 = w.nt * BN;
@@ -324,6 +484,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         }
       }
       // The accumulator is drained: hand it back to the MMA issuer before the slow part below.
+      if (threadIdx.x == 64) BEAM_STAMP(6);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -334,50 +495,27 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       }
       if constexpr (kMode == kModeLayerNorm) {
         // Publish this row's (mean, M2) over the tile, then take the panel's ticket.  The fence before
-        // the barrier orders every epilogue thread's scratch and statistics stores before the ticket.
+        // the barrier orders every epilogue thread's scratch and statistics stores before the ticket;
+        // the thread that draws a panel's last ticket publishes the panel for normalisation.
         if (grow < p.m) p.row_part[static_cast<size_t>(grow) * p.n_tiles + w.nt] = make_float2(st_mean, st_m2);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the 4 epilogue warps only
-        if (warp == 2 && lane == 0) *ticket_slot = atomicAdd(p.tickets + row0 / S::kBM, 1);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const bool last = (*ticket_slot == p.n_tiles - 1);
-        if (last) {
-          __threadfence();
-          // Whole rows per warp, lane = column group: the panel is re-read and the output written in
-          // 512-byte runs.  Every lane merges the row's per-tile statistics in tile order.
-          const int rows_here = min(S::kBM, p.m - row0);
-          for (int r = static_cast<int>(quad); r < rows_here; r += 4) {
-            float n_acc = 0.f, mean = 0.f, m2 = 0.f;
-            const float2* parts = p.row_part + static_cast<size_t>(row0 + r) * p.n_tiles;
-            for (int t = 0; t < p.n_tiles; ++t) {
-              const float2 pt = __ldcg(parts + t);
-              welford_merge(n_acc, mean, m2, static_cast<float>(min(BN, p.n - t * BN)), pt.x, pt.y);
-            }
-            const float rstd = rsqrtf(m2 / n_acc + p.eps);
-            const float* srow = p.scratch + static_cast<size_t>(row0 + r) * p.n;
-            __half* orow = p.c + static_cast<size_t>(row0 + r) * p.ldc;
-            for (int col = static_cast<int>(lane) * 8; col < p.n; col += 256) {
-              const float4 x0 = __ldcg(reinterpret_cast<const float4*>(srow + col));
-              const float4 x1 = __ldcg(reinterpret_cast<const float4*>(srow + col + 4));
-              const uint4 g = __ldg(reinterpret_cast<const uint4*>(p.gamma + col));
-              const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.beta + col));
-              const __half2* g2 = reinterpret_cast<const __half2*>(&g);
-              const __half2* b2 = reinterpret_cast<const __half2*>(&b);
-              const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-              uint32_t o[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float2 gf = __half22float2(g2[q]);
-                const float2 bf = __half22float2(b2[q]);
-                const float y0 = (xs[2 * q] - mean) * rstd * gf.x + bf.x;
-                const float y1 = (xs[2 * q + 1] - mean) * rstd * gf.y + bf.y;
-                o[q] = ptx::pack_half2(y0, y1);
-              }
-              *reinterpret_cast<uint4*>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
+        if (ln_decider && row0 < p.m) {  // a pair's second CTA can sit wholly below the last row
+          const int panel = row0 / S::kBM;
+          if (atomicAdd(p.tickets + panel, 1) == p.n_tiles - 1) {
+            __threadfence();
+            const int slot = atomicAdd(p.ln_queue, 1);
+            *reinterpret_cast<volatile int*>(p.ln_queue + kLnQueueItems + slot) = panel + 1;
           }
         }
+        ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, 0);
       }
+    }
+    if constexpr (kMode == kModeLayerNorm) {
+      // No tiles left: keep normalising until every chunk of the problem has been claimed and this CTA's
+      // own claims are done.  Other CTAs may still be computing, so this is a wait, and it is bounded.
+      const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
+      while (!ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, deadline)) __nanosleep(100);
     }
   }
 
@@ -391,6 +529,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     ptx::tc_fence_after();
     ptx::tmem_dealloc<kCta>(tmem_base, S::kTmemCols);
   }
+  if (threadIdx.x == 0) BEAM_STAMP(7);
 }
 
 // Second kernel of split-K: C[r][c] = fp16( sum over slices, in a fixed order, of partial[s][r][c] ).

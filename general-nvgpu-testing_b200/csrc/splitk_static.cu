@@ -90,6 +90,7 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.scratch = s.scratch;
   p.row_part = nullptr;
   p.tickets = nullptr;
+  p.ln_queue = nullptr;
   p.gamma = nullptr;
   p.beta = nullptr;
   p.eps = 0.f;
@@ -102,6 +103,9 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.group_m = 1;
   p.slices = slices;
   p.status = fault_word;
+#ifdef BEAM_TRACE
+  p.trace = nullptr;
+#endif
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * slices;
   const int ctas = items < s.sm_count ? static_cast<int>(items) : s.sm_count;
   cudaLaunchConfig_t cfg = {};
