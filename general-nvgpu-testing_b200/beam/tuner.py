@@ -101,10 +101,10 @@ class OperatorTuner:
     def _get_gemm_specs(self) -> List[Operator]:
         """Large-GEMM candidates: (tile N, CTAs per tile, ring depth)."""
         search_space = [
-            (256, 2, 4), (256, 2, 6), (256, 2, 7),
+            (256, 2, 4), (256, 2, 5), (256, 2, 6),
             (128, 2, 6), (128, 2, 8),
             (256, 1, 3), (256, 1, 4),
-            (128, 1, 4), (128, 1, 6), (128, 1, 7),
+            (128, 1, 4), (128, 1, 6),
         ]
         ret = [Operator(partial(_C.gemmrc, tile_n=tn, cta_pair=cp, stages=st)) for tn, cp, st in search_space]
         # The reference's own spelling of the tile families (tuner.py:52-59) stays valid.

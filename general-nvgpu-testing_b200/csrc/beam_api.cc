@@ -51,8 +51,10 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.stages = cfg->stages;
     plan.group_m = cfg->group_m;
     plan.max_ctas = cfg->max_ctas;
+    plan.l2_hints = cfg->l2_hints;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
-    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0) return BEAM_ERR_INVALID_ARG;
+    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0 || plan.l2_hints < 0 || plan.l2_hints > 22)
+      return BEAM_ERR_INVALID_ARG;
   }
   return launch_gemmrc(A, B, C, m, n, k, plan, static_cast<cudaStream_t>(stream));
 }

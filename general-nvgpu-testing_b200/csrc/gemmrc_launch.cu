@@ -11,6 +11,8 @@ namespace beam {
 #ifdef BEAM_TRACE
 // Diagnostic builds only (never part of the shipped library): where kernels drop their time stamps.
 static unsigned long long* g_trace_buffer = nullptr;
+static int g_debug_flags = 0;
+extern "C" __attribute__((visibility("default"))) void beam_debug_set_flags(int flags) { g_debug_flags = flags; }
 extern "C" __attribute__((visibility("default"))) void beam_debug_set_trace(unsigned long long* device_buffer) {
   g_trace_buffer = device_buffer;
 }
@@ -24,6 +26,7 @@ struct ExtraArgs {
   const __half* beta = nullptr;
   float eps = 0.f;
   int slices = 1;
+  int l2_hints = 0;
   float2* row_part = nullptr;
   int* tickets = nullptr;
   int* ln_queue = nullptr;
@@ -64,12 +67,20 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     resident = clusters > 0 ? clusters : 1;
   }
 
-  GemmParams p;
+  GemmParams p = {};
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(k), S::kBM, S::kBK, true);
   if (st != BEAM_OK) return st;
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
                       S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  if (kMode == kModeGemm) {
+    st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n),
+                        32, 64, true);
+  } else {
+    st = encode_tmap_3d_f32(&p.tm_s, ex.scratch, static_cast<uint64_t>(ex.slices), static_cast<uint64_t>(m),
+                            static_cast<uint64_t>(n), 32, 32);
+  }
   if (st != BEAM_OK) return st;
   p.c = static_cast<__half*>(C);
   p.scratch = ex.scratch;
@@ -88,9 +99,12 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.n_tiles = (n + BN - 1) / BN;
   p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 8 : 16);
   p.slices = ex.slices;
+  p.hint_a = (ex.l2_hints / 10) % 10;
+  p.hint_b = ex.l2_hints % 10;
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
   p.trace = g_trace_buffer;
+  p.debug = g_debug_flags;
 #endif
 
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
@@ -103,13 +117,20 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kCta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (kMode == kModeSplitK) {
+    // May start while the previous kernel on the stream drains; the kernel itself waits for that grid's
+    // completion before its first global read or write.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
@@ -142,11 +163,11 @@ int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, co
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
-  const ExtraArgs ex;
+  ExtraArgs ex;
+  ex.l2_hints = plan.l2_hints;
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
   BEAM_GEMM_CASE(256, 6, 2)
-  BEAM_GEMM_CASE(256, 7, 2)
   BEAM_GEMM_CASE(128, 4, 2)
   BEAM_GEMM_CASE(128, 6, 2)
   BEAM_GEMM_CASE(128, 8, 2)
@@ -154,7 +175,6 @@ int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, co
   BEAM_GEMM_CASE(256, 4, 1)
   BEAM_GEMM_CASE(128, 4, 1)
   BEAM_GEMM_CASE(128, 6, 1)
-  BEAM_GEMM_CASE(128, 7, 1)
   BEAM_GEMM_CASE(64, 4, 1)
   BEAM_GEMM_CASE(64, 8, 1)
   return BEAM_ERR_UNSUPPORTED;

@@ -8,8 +8,10 @@
 //   warp 1      MMA issuer     one lane of the leader CTA: waits full[s], 4 x tcgen05.mma (K = 16 each)
 //                              per 64-wide k-block into a TMEM accumulator, commits empty[s]; after
 //                              the last k-block commits tmem_full[acc].  Also owns TMEM alloc/dealloc.
-//   warps 2..5  epilogue       wait tmem_full[acc], tcgen05.ld 32 lanes x 32 columns at a time, then
-//                              release the accumulator through tmem_empty[acc].
+//   warps 2..5  epilogue       wait tmem_full[acc], tcgen05.ld 32 lanes x 32 columns at a time, lay each
+//                              row's 128 bytes into a swizzled staging buffer, TMA-store the 32-row box
+//                              (the copy engine clips rows >= M and columns >= N), then release the
+//                              accumulator through tmem_empty[acc].
 //
 // TMEM holds two accumulators (2 x BN fp32 columns) so the epilogue of work item i overlaps the
 // main loop of item i+1.  In pair mode each CTA loads its own 128 rows of A and its own BN/2 rows
@@ -39,6 +41,8 @@ enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2 };
 struct GemmParams {
   CUtensorMap tm_a;  // A  [M, K], box 128 x 64, 128 B swizzle
   CUtensorMap tm_b;  // B  [N, K], box (BN / kCta) x 64, 128 B swizzle
+  CUtensorMap tm_c;  // C  [M, N] fp16, store box 32 rows x 64 columns, 128 B swizzle
+  CUtensorMap tm_s;  // scratch [slices][M][N] fp32, store box 1 x 32 rows x 32 columns, 128 B swizzle
   __half* c;         // fp16 output [M, ldc]
   float* scratch;    // split-K: partials [slices][M][N]; LayerNorm: fp32 panel store [M][N]
   float2* row_part;  // LayerNorm: (mean, M2) of every row over each N tile, [M][n_tiles]
@@ -53,20 +57,38 @@ struct GemmParams {
   int n_tiles;  // tiles of BN columns
   int group_m;  // M-tiles per rasterisation group (GEMM mode)
   int slices;   // split-K slices (1 otherwise)
+  int hint_a;   // L2 eviction policy of the A loads: 0 normal, 1 evict-first, 2 evict-last
+  int hint_b;   // same for the B loads
   int* status;  // device fault word
 #ifdef BEAM_TRACE
-  unsigned long long* trace;  // diagnostic builds only: 8 globaltimer stamps per CTA
+  unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
+  int debug;                  // diagnostic builds only: 1 = skip the output stores, 2 = every tile loads tile (0,0)
 #endif
 };
 
 #ifdef BEAM_TRACE
 #define BEAM_STAMP(slot)                                                                      \
   do {                                                                                        \
-    if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * 8 + (slot)] = ptx::globaltimer_ns(); \
+    if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * 16 + (slot)] = ptx::globaltimer_ns(); \
   } while (0)
+#define BEAM_ACC_BEGIN() const unsigned long long beam_acc_t0 = ptx::globaltimer_ns()
+#define BEAM_ACC_END_T(slot, tid)                                                                                \
+  do {                                                                                                         \
+    if (p.trace && threadIdx.x == (tid)) p.trace[static_cast<size_t>(blockIdx.x) * 16 + (slot)] += ptx::globaltimer_ns() - beam_acc_t0; \
+  } while (0)
+#define BEAM_ACC_END(slot) BEAM_ACC_END_T(slot, 64)
 #else
 #define BEAM_STAMP(slot) \
   do {                   \
+  } while (0)
+#define BEAM_ACC_BEGIN() \
+  do {                   \
+  } while (0)
+#define BEAM_ACC_END(slot) \
+  do {                     \
+  } while (0)
+#define BEAM_ACC_END_T(slot, tid) \
+  do {                            \
   } while (0)
 #endif
 
@@ -80,7 +102,10 @@ struct GemmShape {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kStoreBufBytes = 32 * 128;                // one warp's 32 rows x 128 bytes
+  static constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;   // 4 epilogue warps, double-buffered
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static constexpr int kThreads = 192;
   static_assert(BN == 64 || BN == 128 || BN == 256, "UMMA N of the tile");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
@@ -291,18 +316,21 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   // ---- shared-memory carve-up (tile buffers need 1024-byte alignment for the 128 B swizzle)
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * S::kStageBytes;
+  const uint32_t staging_base = smem_base + kStages * S::kStageBytes;  // 1024-aligned: stage sizes are multiples
+  const uint32_t bar_base = staging_base + S::kStagingBytes;
   auto smem_a = [&](int s) { return smem_base + s * S::kStageBytes; };
   auto smem_b = [&](int s) { return smem_base + s * S::kStageBytes + S::kABytes; };
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* ln_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);  // 4 ints, LayerNorm visits
 
+  const int num_kb = (p.k + S::kBK - 1) / S::kBK;
+  uint32_t preloaded = 0;  // k-blocks of the first work item that thread 0 put in flight during set-up
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
@@ -316,6 +344,29 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
+    if constexpr (kMode == kModeSplitK) {
+      // Launched as a programmatic dependent of the previous call's reduction: everything above may run
+      // while that grid drains; nothing below reads or writes global memory before it has completed.
+      ptx::grid_dependency_wait();
+      // In turn, let this call's reduction kernel become resident early; it blocks until this grid is done.
+      ptx::grid_launch_dependents();
+    }
+    if constexpr (kCta == 1) {
+      // The ring starts empty, so the first loads need no wait: put them in flight before the CTA-wide
+      // set-up barrier (TMEM allocation) instead of after it.  Thread 0 is also the producer thread.
+      WorkItem w0;
+      if (work_item<kMode>(p, first, stride, 0, num_kb, w0)) {
+        const int row_a = w0.mt * S::kBM;
+        const int row_b = w0.nt * BN;
+        for (int kb = w0.kb0; kb < w0.kb1 && preloaded < static_cast<uint32_t>(kStages); ++kb, ++preloaded) {
+          const int s = static_cast<int>(preloaded);
+          ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+          ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, ptx::l2_policy(p.hint_a));
+          ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, ptx::l2_policy(p.hint_b));
+        }
+        BEAM_STAMP(2);
+      }
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc<kCta>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
@@ -327,23 +378,30 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) BEAM_STAMP(1);
-  if constexpr (kMode == kModeSplitK) {
-    // Let the reduction kernel's blocks become resident early; they block until this grid is done.
-    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  }
-
-  const int num_kb = (p.k + S::kBK - 1) / S::kBK;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
+      const uint64_t pol_a = ptx::l2_policy(p.hint_a);
+      const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       WorkItem w;
       for (int j = 0; alive && work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
-        const int row_a = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
-        const int row_b = w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+        int row_a = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
+        int row_b = w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
+#ifdef BEAM_TRACE
+        if (p.debug & 2) {
+          row_a = static_cast<int>(cta_rank) * S::kBM;
+          row_b = static_cast<int>(cta_rank) * S::kBRows;
+        }
+#endif
+        int kb = w.kb0;
+        if (j == 0) {  // these are already in flight
+          kb += static_cast<int>(preloaded);
+          it = preloaded;
+        }
+        for (; kb < w.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {
@@ -352,15 +410,14 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           }
           if constexpr (kCta == 1) {
             ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-            ptx::tma_load_2d(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a);
-            ptx::tma_load_2d(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b);
-            if (it == 0) BEAM_STAMP(2);
+            ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, pol_a);
+            ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
             const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
-            ptx::tma_load_2d_pair(smem_a(s), &p.tm_a, lead_bar, kb * S::kBK, row_a);
-            ptx::tma_load_2d_pair(smem_b(s), &p.tm_b, lead_bar, kb * S::kBK, row_b);
+            ptx::tma_load_2d_pair_hint(smem_a(s), &p.tm_a, lead_bar, kb * S::kBK, row_a, pol_a);
+            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b, lead_bar, kb * S::kBK, row_b, pol_b);
           }
         }
       }
@@ -375,15 +432,25 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       for (int j = 0; alive && work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;
         const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
-        if (!bounded_wait(tmem_empty_bar(acc), acc_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        {
+          BEAM_ACC_BEGIN();
+          const bool drained = bounded_wait(tmem_empty_bar(acc), acc_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
+          BEAM_ACC_END_T(13, 32);
+          if (!drained) break;
+        }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
-          if (!bounded_wait(full_bar(s), ph, cta_abort, p.status, kFaultMmaWaitFull)) {
-            alive = false;
-            break;
+          {
+            BEAM_ACC_BEGIN();
+            const bool landed = bounded_wait(full_bar(s), ph, cta_abort, p.status, kFaultMmaWaitFull);
+            BEAM_ACC_END_T(14, 32);
+            if (!landed) {
+              alive = false;
+              break;
+            }
           }
           ptx::tc_fence_after();
           if (it == 0) BEAM_STAMP(3);
@@ -414,15 +481,24 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are this warp's to read
     const uint32_t row_in_tile = quad * 32u + lane;
     const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    uint32_t store_count = 0;  // bulk stores this warp has issued (selects the staging buffer)
+    if constexpr (kMode == kModeSplitK) ptx::grid_dependency_wait();  // before this thread's first global write
     const bool ln_decider = (warp == 2 && lane == 0);  // LayerNorm: the one thread that talks to the queue
     int ln_pending = -1;                               // LayerNorm: a chunk claimed ahead of its publication
     WorkItem w;
     for (int j = 0; work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
       const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
-      // Every lane polls; the vote keeps the warp together for the .sync.aligned TMEM loads below.
-      const bool ready = bounded_wait(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait);
-      if (!__all_sync(0xffffffffu, ready)) break;
+      // Lane 0 polls (with back-off) for the whole warp, which stays converged for the .sync.aligned TMEM
+      // loads below.
+      bool ready;
+      {
+        BEAM_ACC_BEGIN();
+        ready = bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane);
+        BEAM_ACC_END(8);
+      }
+      if (!ready) break;
+      BEAM_ACC_BEGIN();
       ptx::tc_fence_after();
       if (threadIdx.x == 64) BEAM_STAMP(5);
       const int row0 = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;  // first row of this CTA
@@ -430,60 +506,75 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const int col0 = w.nt * BN;
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
       float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm: this row's statistics over this tile
+      // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
+      constexpr int kChunkCols = (kMode == kModeGemm) ? 64 : 32;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr + c, v);
-        ptx::tmem_ld_wait();
+      for (int c = 0; c < BN; c += kChunkCols) {
+        uint32_t out[32];  // this row's 128 bytes of the chunk
         if constexpr (kMode == kModeGemm) {
-          if (grow < p.m) {
-            __half* crow = p.c + static_cast<size_t>(grow) * p.ldc + col0 + c;
+          uint32_t v0[32], v1[32];
+          ptx::tmem_ld_32x32(taddr + c, v0);
+          ptx::tmem_ld_32x32(taddr + c + 32, v1);
+          ptx::tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (col0 + c + 8 * q < p.n) {  // N % 8 == 0, so a started group of 8 is whole
-                uint4 o;
-                o.x = ptx::pack_half2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-                o.y = ptx::pack_half2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-                o.z = ptx::pack_half2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-                o.w = ptx::pack_half2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-                *reinterpret_cast<uint4*>(crow + 8 * q) = o;
-              }
-            }
+          for (int q = 0; q < 16; ++q) {
+            out[q] = ptx::pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
+            out[16 + q] = ptx::pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
           }
         } else {
-          // fp32 rows: split-K partial of this slice, or the parked LayerNorm panel.
-          if (grow < p.m) {
-            float* srow = p.scratch +
-                          (static_cast<size_t>(w.slice) * p.m + static_cast<size_t>(grow)) * p.n + col0 + c;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              if (col0 + c + 4 * q < p.n) {
-                __stcg(reinterpret_cast<uint4*>(srow + 4 * q),
-                       make_uint4(v[4 * q + 0], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-              }
-            }
-          }
+          ptx::tmem_ld_32x32(taddr + c, out);
+          ptx::tmem_ld_wait();
           if constexpr (kMode == kModeLayerNorm) {
             // Two-pass statistics of the (up to) 32 values in registers, merged into the row's running
             // (count, mean, M2).  Columns past N do not exist and are left out.
             const int valid = min(32, p.n - (col0 + c));
             if (valid > 0) {
-              float s = 0.f;
+              float sum = 0.f;
 #pragma unroll
-              for (int q = 0; q < 32; ++q) s += (q < valid) ? __uint_as_float(v[q]) : 0.f;
-              const float mb = s / static_cast<float>(valid);
+              for (int q = 0; q < 32; ++q) sum += (q < valid) ? __uint_as_float(out[q]) : 0.f;
+              const float mb = sum / static_cast<float>(valid);
               float m2b = 0.f;
 #pragma unroll
               for (int q = 0; q < 32; ++q) {
-                const float d = __uint_as_float(v[q]) - mb;
+                const float d = __uint_as_float(out[q]) - mb;
                 m2b += (q < valid) ? d * d : 0.f;
               }
               welford_merge(st_n, st_mean, st_m2, static_cast<float>(valid), mb, m2b);
             }
           }
         }
+        bool box_live = col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m;  // warp-uniform
+#ifdef BEAM_TRACE
+        if (p.debug & 1) box_live = false;
+#endif
+        if (box_live) {
+          // Before a staging buffer is rewritten, the bulk store that last read it must be done reading.
+          const uint32_t buf = staging_base + (quad * 2u + (store_count & 1u)) * S::kStoreBufBytes;
+          if (store_count >= 2) {
+            if (lane == 0) ptx::tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          // Row `lane` of the box, 16-byte piece j at (j ^ (lane & 7)): the 128-byte swizzle the copy
+          // engine expects, which also spreads each quarter-warp's stores over all banks.
+          const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4), out[4 * j], out[4 * j + 1],
+                              out[4 * j + 2], out[4 * j + 3]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kMode == kModeGemm)
+              ptx::tma_store_2d(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
+            else
+              ptx::tma_store_3d(&p.tm_s, buf, col0 + c, row0 + static_cast<int>(quad) * 32, w.slice);
+            ptx::tma_store_commit();
+          }
+          ++store_count;
+        }
       }
       // The accumulator is drained: hand it back to the MMA issuer before the slow part below.
+      BEAM_ACC_END(9);
       if (threadIdx.x == 64) BEAM_STAMP(6);
       ptx::tc_fence_before();
       __syncwarp();
@@ -497,7 +588,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         // Publish this row's (mean, M2) over the tile, then take the panel's ticket.  The fence before
         // the barrier orders every epilogue thread's scratch and statistics stores before the ticket;
         // the thread that draws a panel's last ticket publishes the panel for normalisation.
+        BEAM_ACC_BEGIN();
         if (grow < p.m) p.row_part[static_cast<size_t>(grow) * p.n_tiles + w.nt] = make_float2(st_mean, st_m2);
+        if (lane == 0) ptx::tma_store_wait_all<0>();  // this warp's parked rows have landed in global memory
+        __syncwarp();
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the 4 epilogue warps only
         if (ln_decider && row0 < p.m) {  // a pair's second CTA can sit wholly below the last row
@@ -508,18 +602,27 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             *reinterpret_cast<volatile int*>(p.ln_queue + kLnQueueItems + slot) = panel + 1;
           }
         }
-        ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, 0);
+        BEAM_ACC_END(10);
+        {
+          BEAM_ACC_BEGIN();
+          ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, 0);
+          BEAM_ACC_END(11);
+        }
       }
     }
     if constexpr (kMode == kModeLayerNorm) {
       // No tiles left: keep normalising until every chunk of the problem has been claimed and this CTA's
       // own claims are done.  Other CTAs may still be computing, so this is a wait, and it is bounded.
+      BEAM_ACC_BEGIN();
       const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
       while (!ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, deadline)) __nanosleep(100);
+      BEAM_ACC_END(12);
     }
   }
 
-  // ---- teardown: everyone meets, then the allocating warp frees TMEM
+  // ---- teardown: bulk stores must have finished reading shared memory (and, for the kernels that follow,
+  // writing global memory) before the CTA goes away; then everyone meets and the allocating warp frees TMEM
+  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
   __syncwarp();
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();
@@ -538,8 +641,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
 // depends only on the slice count, never on timing, so results are bitwise reproducible.
 constexpr int kReduceGroups = 8;
 static __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial,
-                                                            __half* __restrict__ c, int m, int n, int slices) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // partials of the producing kernel are complete
+                                                                   __half* __restrict__ c, int m, int n,
+                                                                   int slices) {
+  ptx::grid_launch_dependents();  // the next call's first kernel may set itself up while this grid runs
+  ptx::grid_dependency_wait();    // partials of the producing kernel are complete and visible
   __shared__ float4 sums[kReduceGroups][32];
   const int q = threadIdx.x & 31;
   const int g = threadIdx.x >> 5;
@@ -552,20 +657,19 @@ static __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* 
     const int s1 = slices * (g + 1) / kReduceGroups;
     const size_t plane = static_cast<size_t>(m) * n;
     const float* src = partial + static_cast<size_t>(row) * n + col;
-    int s = s0;
-    for (; s + 4 <= s1; s += 4) {
-      const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + plane * s));
-      const float4 v1 = __ldcg(reinterpret_cast<const float4*>(src + plane * (s + 1)));
-      const float4 v2 = __ldcg(reinterpret_cast<const float4*>(src + plane * (s + 2)));
-      const float4 v3 = __ldcg(reinterpret_cast<const float4*>(src + plane * (s + 3)));
-      acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
-      acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
-      acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
-      acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
-    }
-    for (; s < s1; ++s) {
-      const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + plane * s));
-      acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+    constexpr int kBatch = 8;  // independent loads in flight; the additions stay in ascending slice order
+    for (int s = s0; s < s1; s += kBatch) {
+      float4 v[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i)
+        v[i] = (s + i < s1) ? __ldcg(reinterpret_cast<const float4*>(src + plane * (s + i)))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        if (s + i < s1) {
+          acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w;
+        }
+      }
     }
   }
   sums[g][q] = acc;

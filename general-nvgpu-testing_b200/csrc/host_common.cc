@@ -103,4 +103,24 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
   return BEAM_OK;
 }
 
+// 3-D row-major fp32 tensor [planes][rows][cols] (dense), box = 1 x box_rows x box_cols, 128-byte swizzle.
+int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return BEAM_ERR_TENSORMAP;
+  const cuuint64_t gdim[3] = {cols, rows, planes};
+  const cuuint64_t gstride[2] = {cols * 4, rows * cols * 4};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), gdim, gstride, box, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled (3-D) failed with CUresult %d",
+                  static_cast<int>(r));
+    return BEAM_ERR_TENSORMAP;
+  }
+  return BEAM_OK;
+}
+
 }  // namespace beam

@@ -31,6 +31,10 @@ DeviceCtx* current_device_ctx(int* err);
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                    uint32_t box_rows, uint32_t box_cols, bool swizzle128);
 
+// Dense 3-D fp32 tensor [planes][rows][cols], box 1 x box_rows x box_cols (box_cols * 4 = 128 B), 128-byte swizzle.
+int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows, uint32_t box_cols);
+
 // Records a CUDA runtime failure for beam_last_cuda_error() (thread-local text).
 void note_cuda_error(cudaError_t e, const char* where);
 const char* last_cuda_error_text();

@@ -79,12 +79,15 @@ template <int BN, int kStages>
 int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C, int m, int n, int k, int slices,
                     int* fault_word, cudaStream_t stream) {
   using S = GemmShape<BN, kStages, 1>;
-  GemmParams p;
+  GemmParams p = {};
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(k), S::kBM, S::kBK, true);
   if (st != BEAM_OK) return st;
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
                       S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_3d_f32(&p.tm_s, s.scratch, static_cast<uint64_t>(slices), static_cast<uint64_t>(m),
+                          static_cast<uint64_t>(n), 32, 32);
   if (st != BEAM_OK) return st;
   p.c = static_cast<__half*>(C);
   p.scratch = s.scratch;
@@ -102,9 +105,12 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.n_tiles = (n + BN - 1) / BN;
   p.group_m = 1;
   p.slices = slices;
+  p.hint_a = 0;
+  p.hint_b = 0;
   p.status = fault_word;
 #ifdef BEAM_TRACE
   p.trace = nullptr;
+  p.debug = 0;
 #endif
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * slices;
   const int ctas = items < s.sm_count ? static_cast<int>(items) : s.sm_count;

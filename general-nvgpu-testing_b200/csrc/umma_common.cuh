@@ -43,6 +43,40 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   }
 }
 
+// The same wait for roles that can afford a slower wake-up (the epilogue, whose accumulator is
+// double-buffered): only lane 0 polls, backing off with nanosleep between polls, and the rest of the warp
+// parks at a warp barrier instead of spinning.  Returns the same value in every lane.
+__device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, volatile int* cta_abort,
+                                                  int* status_word, int fault, uint32_t lane) {
+  int ok = 1;
+  if (lane == 0) {
+    if (!ptx::mbar_try_wait(bar, parity)) {
+      uint64_t t0 = 0;
+      for (uint32_t spin = 1;; ++spin) {
+        __nanosleep(128);
+        if (ptx::mbar_try_wait(bar, parity)) break;
+        if ((spin & 0x3FFu) == 0) {
+          if (*cta_abort) {
+            ok = 0;
+            break;
+          }
+          const uint64_t now = ptx::globaltimer_ns();
+          if (t0 == 0) {
+            t0 = now;
+          } else if (now - t0 > kWaitLimitNs) {
+            *cta_abort = 1;
+            if (status_word) atomicCAS(status_word, 0, fault);
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 // After an abort, give asynchronous work this CTA already issued (TMA copies into its shared
 // memory, UMMAs into its TMEM) time to land before shared memory and TMEM are released.
 __device__ __forceinline__ void abort_drain_delay() {

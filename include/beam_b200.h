@@ -54,7 +54,9 @@ typedef struct beam_gemm_cfg {
   int group_m;        /* tile rasterisation: M-tiles per L2 group                              */
   int split_k_slices; /* split-K only: number of K slices (0 = heuristic)                      */
   int max_ctas;       /* cap on the persistent grid (0 = all SMs)                              */
-  int reserved[2];
+  int l2_hints;       /* L2 eviction policy of the TMA loads, two decimal digits: tens = A, ones = B;
+                         0 normal, 1 evict-first, 2 evict-last (e.g. 21 = keep A, stream B)          */
+  int reserved[1];
 } beam_gemm_cfg;
 
 BEAM_API const char* beam_status_string(int status);
