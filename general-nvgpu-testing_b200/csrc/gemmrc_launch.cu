@@ -35,7 +35,7 @@ struct ExtraArgs {
 template <int BN, int kStages, int kCta, int kMode>
 int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
                     int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
-  using S = GemmShape<BN, kStages, kCta>;
+  using S = GemmShape<BN, kStages, kCta, kMode>;
   auto kernel = gemmrc_umma_kernel<BN, kStages, kCta, kMode>;
 
   // One-time per (instantiation, device): opt in to the large dynamic shared memory and, for
@@ -317,9 +317,15 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   BEAM_CUDA_TRY(cudaMemsetAsync(ex.tickets, 0, l.ticket_bytes, stream), "cudaMemsetAsync(tickets)");
   // CTA pairs on 256-row tiles once there are enough tiles to fill the device; single CTAs otherwise.
   const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + kLnTileN - 1) / kLnTileN);
-  if (pair_tiles >= ctx->sm_count / 2)
-    return launch_instance<kLnTileN, 6, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, 0, 0, ex, stream);
-  return launch_instance<kLnTileN, 4, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, 0, 0, ex, stream);
+  // Rasterisation: one wave of resident CTAs should cover whole rows of tiles, so that a panel's N tiles are
+  // computed close together in time and its parked values are still in L2 when they are normalised.
+  const int n_tiles = (n + kLnTileN - 1) / kLnTileN;
+  if (pair_tiles >= ctx->sm_count / 2) {
+    const int group_m = (ctx->sm_count / 2 + n_tiles - 1) / n_tiles;
+    return launch_instance<kLnTileN, 5, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, group_m, 0, ex, stream);
+  }
+  const int group_m = (ctx->sm_count + n_tiles - 1) / n_tiles;
+  return launch_instance<kLnTileN, 3, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, group_m, 0, ex, stream);
 }
 
 }  // namespace beam

@@ -92,7 +92,7 @@ struct GemmParams {
   } while (0)
 #endif
 
-template <int BN, int kStages, int kCta>
+template <int BN, int kStages, int kCta, int kMode = kModeGemm>
 struct GemmShape {
   static constexpr int kBM = 128;
   static constexpr int kBK = 64;
@@ -101,15 +101,19 @@ struct GemmShape {
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
-  static constexpr int kBarBytes = 256;
-  static constexpr int kStoreBufBytes = 32 * 128;                // one warp's 32 rows x 128 bytes
-  static constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;   // 4 epilogue warps, double-buffered
+  static constexpr int kBarBytes = 512;
+  static constexpr int kStoreBufBytes = 32 * 128;  // one warp's box: 32 rows x 128 bytes
+  // Staging buffers per epilogue warp: two for the output stores; LayerNorm keeps four, which also serve
+  // as the landing ring of its second pass.
+  static constexpr int kBufsPerWarp = (kMode == kModeLayerNorm) ? 4 : 2;
+  static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
-  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static constexpr int kThreads = 192;
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static_assert(BN == 64 || BN == 128 || BN == 256, "UMMA N of the tile");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
-  static_assert((2 * kStages + 4) * 8 + 32 <= kBarBytes, "barrier block too small");  // + tmem, abort, 4 slots
+  // mbarriers: full/empty per stage, 2 + 2 for TMEM, 16 for the LayerNorm landing ring; then 8 ints.
+  static_assert((2 * kStages + 4 + 16) * 8 + 32 <= kBarBytes, "barrier block too small");
 };
 
 struct WorkItem {
@@ -166,143 +170,157 @@ __device__ __forceinline__ void welford_merge(float& n, float& mean, float& m2, 
 }
 
 // ------------------------------------------------------------------ LayerNorm second pass
-constexpr int kLnChunkRows = 8;                        // rows per claimed chunk: two per epilogue warp
-constexpr int kLnChunksPerPanel = 128 / kLnChunkRows;  // a panel is 128 rows
-constexpr int kLnQueueItems = 16;                      // int offset of the published-panel list
+// Work unit of the second pass: 32 rows x 512 columns of a published panel, normalised by one warp.
+constexpr int kLnUnitCols = 512;
+constexpr int kLnQueueItems = 16;  // int offset of the published-panel list inside the queue block
 
 __device__ __forceinline__ int ld_volatile_i32(const int* ptr) {
   return *reinterpret_cast<const volatile int*>(ptr);
 }
+__device__ __forceinline__ int ln_units_per_panel(int n) { return 4 * ((n + kLnUnitCols - 1) / kLnUnitCols); }
 
-// One warp normalises one complete output row: merges the row's per-tile (mean, M2) in tile order
-// (lanes fetch 32 tiles at a time, then every lane replays the same merge sequence from shuffles),
-// then streams the parked fp32 row with 16 independent 16-byte loads in flight per lane.
+// One warp normalises unit `u` of the panel published in queue slot `slot`: lane = row.  Each lane merges its
+// row's per-tile (mean, M2) in tile order, then the parked fp32 values come back through TMA as 32 x 32 boxes
+// into the warp's four staging buffers (a four-deep ring, so three boxes are in flight while one is being
+// consumed); every lane reads its row's 128 bytes, applies (x - mean) * rstd * gamma + beta and stores 64 bytes
+// of fp16.  ring_count counts the boxes this warp has ever landed (selects buffer and mbarrier parity).
 template <int BN>
-__device__ __forceinline__ void ln_normalise_row(const GemmParams& p, int row, uint32_t lane) {
-  float n_acc = 0.f, mean = 0.f, m2 = 0.f;
-  const float2* parts = p.row_part + static_cast<size_t>(row) * p.n_tiles;
-  for (int t0 = 0; t0 < p.n_tiles; t0 += 32) {
-    const int t = t0 + static_cast<int>(lane);
-    float2 mine = make_float2(0.f, 0.f);
-    if (t < p.n_tiles) mine = __ldcg(parts + t);
-    const int cnt = min(32, p.n_tiles - t0);
-    for (int i = 0; i < cnt; ++i) {
-      const float mb = __shfl_sync(0xffffffffu, mine.x, i);
-      const float m2b = __shfl_sync(0xffffffffu, mine.y, i);
-      welford_merge(n_acc, mean, m2, static_cast<float>(min(BN, p.n - (t0 + i) * BN)), mb, m2b);
-    }
+__device__ __forceinline__ void ln_normalise_unit(const GemmParams& p, int panel, int u, uint32_t lane,
+                                                  uint32_t buf_base, uint32_t bar_base, uint32_t& ring_count,
+                                                  volatile int* cta_abort) {
+  const int col_units = (p.n + kLnUnitCols - 1) / kLnUnitCols;
+  const int row_base = panel * 128 + (u / col_units) * 32;
+  const int col_base = (u % col_units) * kLnUnitCols;
+  if (row_base >= p.m) return;
+  const int boxes = (min(p.n, col_base + kLnUnitCols) - col_base + 31) / 32;
+  auto issue = [&](int i) {  // lane 0 only
+    const uint32_t k = ring_count + static_cast<uint32_t>(i);
+    const uint32_t bar = bar_base + 8u * (k & 3u);
+    ptx::mbar_arrive_expect_tx(bar, 4096);
+    ptx::tma_load_3d(buf_base + (k & 3u) * 4096u, &p.tm_s, bar, col_base + i * 32, row_base, 0);
+  };
+  if (lane == 0) {
+    for (int i = 0; i < min(4, boxes); ++i) issue(i);
   }
-  const float rstd = rsqrtf(m2 / n_acc + p.eps);
-  const float* srow = p.scratch + static_cast<size_t>(row) * p.n;
+  // Statistics of this lane's row while the first boxes fly.
+  const int row = row_base + static_cast<int>(lane);
+  float mean = 0.f, rstd = 0.f;
+  if (row < p.m) {
+    float n_acc = 0.f, m2 = 0.f;
+    const float2* parts = p.row_part + static_cast<size_t>(row) * p.n_tiles;
+    for (int t0 = 0; t0 < p.n_tiles; t0 += 8) {
+      float2 pt[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pt[i] = (t0 + i < p.n_tiles) ? __ldcg(parts + t0 + i) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (t0 + i < p.n_tiles)
+          welford_merge(n_acc, mean, m2, static_cast<float>(min(BN, p.n - (t0 + i) * BN)), pt[i].x, pt[i].y);
+    }
+    rstd = rsqrtf(m2 / n_acc + p.eps);
+  }
   __half* orow = p.c + static_cast<size_t>(row) * p.ldc;
-  constexpr int kUnits = 8;  // 8 columns per unit and lane: 2048 columns per sweep of the warp
-  for (int base = 0; base < p.n; base += 256 * kUnits) {
-    float4 x0[kUnits], x1[kUnits];
+  for (int i = 0; i < boxes; ++i) {
+    const uint32_t k = ring_count + static_cast<uint32_t>(i);
+    const uint32_t buf = buf_base + (k & 3u) * 4096u;
+    if (!bounded_wait_warp(bar_base + 8u * (k & 3u), (k >> 2) & 1u, cta_abort, p.status, kFaultReduceWait, lane))
+      break;
+    uint4 x[8];
 #pragma unroll
-    for (int u = 0; u < kUnits; ++u) {
-      const int col = base + u * 256 + static_cast<int>(lane) * 8;
-      x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (col < p.n) {
-        x0[u] = __ldcg(reinterpret_cast<const float4*>(srow + col));
-        x1[u] = __ldcg(reinterpret_cast<const float4*>(srow + col + 4));
-      }
-    }
+    for (int j = 0; j < 8; ++j) x[j] = ptx::ld_shared_v4(buf + lane * 128u + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4));
+    // The buffer may be refilled once every lane has read it; the fence orders these generic reads before
+    // the copy engine's writes.
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && i + 4 < boxes) issue(i + 4);
+    const int col = col_base + i * 32;
+    if (row < p.m) {
 #pragma unroll
-    for (int u = 0; u < kUnits; ++u) {
-      const int col = base + u * 256 + static_cast<int>(lane) * 8;
-      if (col < p.n) {
-        const uint4 g = __ldg(reinterpret_cast<const uint4*>(p.gamma + col));
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.beta + col));
-        const __half2* g2 = reinterpret_cast<const __half2*>(&g);
-        const __half2* b2 = reinterpret_cast<const __half2*>(&b);
-        const float xs[8] = {x0[u].x, x0[u].y, x0[u].z, x0[u].w, x1[u].x, x1[u].y, x1[u].z, x1[u].w};
-        uint32_t o[4];
+      for (int j = 0; j < 4; ++j) {  // 8 columns per step
+        if (col + 8 * j < p.n) {
+          const uint4 g = __ldg(reinterpret_cast<const uint4*>(p.gamma + col + 8 * j));
+          const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.beta + col + 8 * j));
+          const __half2* g2 = reinterpret_cast<const __half2*>(&g);
+          const __half2* b2 = reinterpret_cast<const __half2*>(&b);
+          const uint32_t xs[8] = {x[2 * j].x, x[2 * j].y, x[2 * j].z, x[2 * j].w,
+                                  x[2 * j + 1].x, x[2 * j + 1].y, x[2 * j + 1].z, x[2 * j + 1].w};
+          uint32_t o[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 gf = __half22float2(g2[q]);
-          const float2 bf = __half22float2(b2[q]);
-          o[q] = ptx::pack_half2((xs[2 * q] - mean) * rstd * gf.x + bf.x, (xs[2 * q + 1] - mean) * rstd * gf.y + bf.y);
+          for (int q = 0; q < 4; ++q) {
+            const float2 gf = __half22float2(g2[q]);
+            const float2 bf = __half22float2(b2[q]);
+            o[q] = ptx::pack_half2((__uint_as_float(xs[2 * q]) - mean) * rstd * gf.x + bf.x,
+                                   (__uint_as_float(xs[2 * q + 1]) - mean) * rstd * gf.y + bf.y);
+          }
+          *reinterpret_cast<uint4*>(orow + col + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        *reinterpret_cast<uint4*>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   }
+  ring_count += static_cast<uint32_t>(boxes);
 }
 
-// One visit of the four epilogue warps to the device-wide queue of panels whose statistics are complete.
-// The deciding thread (decider == true for exactly one of the 128 threads) claims up to two chunks with
-// atomicAdd on the claim counter and posts them in `slots`; all four warps then normalise them, two rows
-// per warp and chunk.  A claim can run ahead of publication (the counter is bumped before the panel it
-// falls into is published): such a chunk is kept in `pending` and retried at the next visit.
-// slots: [0] chunks to do now, [1], [2] their ids, [3] 1 = every chunk of the problem has been claimed and
-// this CTA holds no pending claim.
-// deadline_ns != 0 (the drain after the last tile): past it, or once the CTA has aborted, the decider
-// reports a fault and tells everyone to leave.
+// One visit of a warp to the device-wide queue of panels whose statistics are complete.  Lane 0 claims at
+// most one unit with atomicAdd on the claim counter.  A claim can run ahead of publication (the counter is
+// bumped before the panel it falls into is published): such a unit stays in `pending` and is retried at the
+// next visit.  Returns kLnWorked after normalising a unit, kLnAllDone when every unit of the problem has been
+// claimed and this warp holds none, kLnIdle otherwise.
+// deadline_ns != 0 (the drain after the last tile): past it, or once the CTA has aborted, report kLnAllDone.
+enum LnVisit : int { kLnIdle = 0, kLnWorked = 1, kLnAllDone = 2 };
 template <int BN>
-__device__ __forceinline__ bool ln_visit(const GemmParams& p, volatile int* slots, int& pending, bool decider,
-                                         uint32_t quad, uint32_t lane, volatile int* cta_abort,
+__device__ __forceinline__ int ln_visit(const GemmParams& p, int& pending, uint32_t lane, uint32_t buf_base,
+                                         uint32_t bar_base, uint32_t& ring_count, volatile int* cta_abort,
                                          uint64_t deadline_ns) {
   int* q = p.ln_queue;
-  const int panels = (p.m + 127) / 128;
-  const int total_chunks = panels * kLnChunksPerPanel;
-  if (decider) {
-    auto ready = [&](int c) {
-      const int slot = c / kLnChunksPerPanel;
-      return slot < ld_volatile_i32(q) && ld_volatile_i32(q + kLnQueueItems + slot) != 0;
-    };
-    int count = 0;
-    if (pending >= 0 && ready(pending)) {
-      slots[1 + count++] = pending;
-      pending = -1;
-    }
-    bool exhausted = false;
-    while (count < 2 && pending < 0) {
+  const int upp = ln_units_per_panel(p.n);
+  const int total = ((p.m + 127) / 128) * upp;
+  int unit = -1, panel = 0, done = 0;
+  if (lane == 0) {
+    if (pending < 0) {
       const int head = ld_volatile_i32(q + 1);
-      if (head >= total_chunks) {
-        exhausted = true;
-        break;
+      if (head >= total) {
+        done = 1;
+      } else if (head < ld_volatile_i32(q) * upp) {
+        const int c = atomicAdd(q + 1, 1);
+        if (c >= total)
+          done = 1;
+        else
+          pending = c;
       }
-      if (head >= ld_volatile_i32(q) * kLnChunksPerPanel) break;  // nothing published beyond the claims
-      const int c = atomicAdd(q + 1, 1);
-      if (c >= total_chunks) {
-        exhausted = true;
-        break;
-      }
-      if (ready(c))
-        slots[1 + count++] = c;
-      else
-        pending = c;
     }
-    slots[0] = count;
-    slots[3] = (exhausted && pending < 0) ? 1 : 0;
-    if (deadline_ns != 0 && count == 0 && slots[3] == 0) {
+    if (pending >= 0) {
+      const int slot = pending / upp;
+      if (slot < ld_volatile_i32(q)) {
+        const int item = ld_volatile_i32(q + kLnQueueItems + slot);
+        if (item != 0) {
+          unit = pending % upp;
+          panel = item - 1;
+          pending = -1;
+        }
+      }
+    }
+    if (deadline_ns != 0 && unit < 0 && !done) {
       if (!*cta_abort && ptx::globaltimer_ns() > deadline_ns) {
         *cta_abort = 1;
         if (p.status) atomicCAS(p.status, 0, static_cast<int>(kFaultReduceWait));
       }
-      if (*cta_abort) slots[3] = 1;
+      if (*cta_abort) done = 1;
     }
   }
-  asm volatile("bar.sync 1, 128;" ::: "memory");
-  const int count = slots[0];
-  const bool all_claimed = slots[3] != 0;
-  if (count > 0) {
+  unit = __shfl_sync(0xffffffffu, unit, 0);
+  panel = __shfl_sync(0xffffffffu, panel, 0);
+  done = __shfl_sync(0xffffffffu, done, 0);
+  if (unit >= 0) {
     __threadfence();  // acquire side of the publication: panel data and statistics are visible below
-    for (int i = 0; i < count; ++i) {
-      const int c = slots[1 + i];
-      const int panel = ld_volatile_i32(q + kLnQueueItems + c / kLnChunksPerPanel) - 1;
-      const int row0 = panel * 128 + (c % kLnChunksPerPanel) * kLnChunkRows + static_cast<int>(quad) * 2;
-      if (row0 < p.m) ln_normalise_row<BN>(p, row0, lane);
-      if (row0 + 1 < p.m) ln_normalise_row<BN>(p, row0 + 1, lane);
-    }
+    ln_normalise_unit<BN>(p, panel, unit, lane, buf_base, bar_base, ring_count, cta_abort);
+    return kLnWorked;
   }
-  asm volatile("bar.sync 1, 128;" ::: "memory");  // slots may be rewritten by the next visit
-  return all_claimed && count == 0;
+  return done != 0 ? kLnAllDone : kLnIdle;
 }
 
 template <int BN, int kStages, int kCta, int kMode>
 __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmShape<BN, kStages, kCta>;
+  using S = GemmShape<BN, kStages, kCta, kMode>;
   extern __shared__ uint8_t smem_raw[];
 
   const uint32_t warp = threadIdx.x >> 5;
@@ -324,10 +342,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto ln_ring_bar = [&](uint32_t quad_) { return bar_base + 8u * (2 * kStages + 4 + 4 * quad_); };  // 4 per warp
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
-      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4));
+      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4 + 16));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* ln_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);  // 4 ints, LayerNorm visits
 
   const int num_kb = (p.k + S::kBK - 1) / S::kBK;
   uint32_t preloaded = 0;  // k-blocks of the first work item that thread 0 put in flight during set-up
@@ -339,6 +357,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
       ptx::mbar_init(tmem_empty_bar(a), 4 * kCta);  // one arrive per epilogue warp of each CTA
+    }
+    if constexpr (kMode == kModeLayerNorm) {
+      for (uint32_t i = 0; i < 16; ++i) ptx::mbar_init(ln_ring_bar(0) + 8u * i, 1);
     }
     *cta_abort = 0;
     ptx::fence_mbar_init();
@@ -483,8 +504,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
     uint32_t store_count = 0;  // bulk stores this warp has issued (selects the staging buffer)
     if constexpr (kMode == kModeSplitK) ptx::grid_dependency_wait();  // before this thread's first global write
-    const bool ln_decider = (warp == 2 && lane == 0);  // LayerNorm: the one thread that talks to the queue
-    int ln_pending = -1;                               // LayerNorm: a chunk claimed ahead of its publication
+    int ln_pending = -1;                               // LayerNorm: a unit this warp claimed ahead of its publication
+    uint32_t ln_ring_count = 0;                        // LayerNorm: boxes this warp's landing ring has received
+    const uint32_t ln_bufs = staging_base + quad * S::kBufsPerWarp * S::kStoreBufBytes;
     WorkItem w;
     for (int j = 0; work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
@@ -492,7 +514,43 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // Lane 0 polls (with back-off) for the whole warp, which stays converged for the .sync.aligned TMEM
       // loads below.
       bool ready;
-      {
+      if constexpr (kMode == kModeLayerNorm) {
+        // While the accumulator is not ready, this warp spends the time on the second pass: one unit of a
+        // published panel per iteration (its staging buffers are idle: its stores have completed).
+        BEAM_ACC_BEGIN();
+        const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
+        bool pass2_done = false;
+        for (;;) {
+          int hit = 0;
+          if (lane == 0) hit = ptx::mbar_try_wait(tmem_full_bar(acc), acc_ph) ? 1 : 0;
+          hit = __shfl_sync(0xffffffffu, hit, 0);
+          if (hit) {
+            ready = true;
+            break;
+          }
+          int did = kLnIdle;
+          if (!pass2_done) {
+            did = ln_visit<BN>(p, ln_pending, lane, ln_bufs, ln_ring_bar(quad), ln_ring_count, cta_abort, 0);
+            pass2_done = did == kLnAllDone;
+          }
+          if (did != kLnWorked) {
+            __nanosleep(128);
+            int give_up = 0;
+            if (lane == 0) {
+              if (!*cta_abort && ptx::globaltimer_ns() > deadline) {
+                *cta_abort = 1;
+                if (p.status) atomicCAS(p.status, 0, static_cast<int>(kFaultEpilogueWait));
+              }
+              give_up = *cta_abort;
+            }
+            if (__shfl_sync(0xffffffffu, give_up, 0)) {
+              ready = false;
+              break;
+            }
+          }
+        }
+        BEAM_ACC_END(8);
+      } else {
         BEAM_ACC_BEGIN();
         ready = bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane);
         BEAM_ACC_END(8);
@@ -549,9 +607,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
 #endif
         if (box_live) {
           // Before a staging buffer is rewritten, the bulk store that last read it must be done reading.
-          const uint32_t buf = staging_base + (quad * 2u + (store_count & 1u)) * S::kStoreBufBytes;
-          if (store_count >= 2) {
-            if (lane == 0) ptx::tma_store_wait_read<1>();
+          constexpr uint32_t kBufs = S::kBufsPerWarp;
+          const uint32_t buf = staging_base + (quad * kBufs + (store_count % kBufs)) * S::kStoreBufBytes;
+          if (store_count >= kBufs) {
+            if (lane == 0) ptx::tma_store_wait_read<kBufs - 1>();
             __syncwarp();
           }
           // Row `lane` of the box, 16-byte piece j at (j ^ (lane & 7)): the 128-byte swizzle the copy
@@ -585,37 +644,36 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::mbar_arrive_cluster(lead_empty0 + 8u * acc);
       }
       if constexpr (kMode == kModeLayerNorm) {
-        // Publish this row's (mean, M2) over the tile, then take the panel's ticket.  The fence before
-        // the barrier orders every epilogue thread's scratch and statistics stores before the ticket;
-        // the thread that draws a panel's last ticket publishes the panel for normalisation.
+        // Publish this row's (mean, M2) over the tile; once this warp's parked rows have landed, fence and take
+        // one of the panel's tickets (four per tile, one per epilogue warp).  The warp that draws the panel's
+        // last ticket publishes it for normalisation.
         BEAM_ACC_BEGIN();
         if (grow < p.m) p.row_part[static_cast<size_t>(grow) * p.n_tiles + w.nt] = make_float2(st_mean, st_m2);
-        if (lane == 0) ptx::tma_store_wait_all<0>();  // this warp's parked rows have landed in global memory
+        if (lane == 0) ptx::tma_store_wait_all<0>();
         __syncwarp();
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the 4 epilogue warps only
-        if (ln_decider && row0 < p.m) {  // a pair's second CTA can sit wholly below the last row
+        __syncwarp();
+        if (lane == 0 && row0 < p.m) {  // a pair's second CTA can sit wholly below the last row
           const int panel = row0 / S::kBM;
-          if (atomicAdd(p.tickets + panel, 1) == p.n_tiles - 1) {
+          if (atomicAdd(p.tickets + panel, 1) == 4 * p.n_tiles - 1) {
             __threadfence();
             const int slot = atomicAdd(p.ln_queue, 1);
             *reinterpret_cast<volatile int*>(p.ln_queue + kLnQueueItems + slot) = panel + 1;
           }
         }
         BEAM_ACC_END(10);
-        {
-          BEAM_ACC_BEGIN();
-          ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, 0);
-          BEAM_ACC_END(11);
-        }
       }
     }
     if constexpr (kMode == kModeLayerNorm) {
-      // No tiles left: keep normalising until every chunk of the problem has been claimed and this CTA's
-      // own claims are done.  Other CTAs may still be computing, so this is a wait, and it is bounded.
+      // No tiles left: keep normalising until every unit of the problem has been claimed and this warp's own
+      // claim is done.  Other CTAs may still be computing, so this is a wait, and it is bounded.
       BEAM_ACC_BEGIN();
       const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
-      while (!ln_visit<BN>(p, ln_slots, ln_pending, ln_decider, quad, lane, cta_abort, deadline)) __nanosleep(100);
+      for (;;) {
+        const int did = ln_visit<BN>(p, ln_pending, lane, ln_bufs, ln_ring_bar(quad), ln_ring_count, cta_abort, deadline);
+        if (did == kLnAllDone) break;
+        if (did == kLnIdle) __nanosleep(100);
+      }
       BEAM_ACC_END(12);
     }
   }

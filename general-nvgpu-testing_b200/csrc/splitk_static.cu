@@ -45,8 +45,8 @@ struct StaticSetup {
 StaticSetup g_setup[64];
 std::mutex g_setup_mutex;
 
-using Kernel64 = GemmShape<64, 8, 1>;
-using Kernel128 = GemmShape<128, 6, 1>;
+using Kernel64 = GemmShape<64, 8, 1, kModeSplitK>;
+using Kernel128 = GemmShape<128, 6, 1, kModeSplitK>;
 
 // One-time per device, with that device current.
 int setup_device(int dev, StaticSetup** out) {
@@ -78,7 +78,7 @@ int setup_device(int dev, StaticSetup** out) {
 template <int BN, int kStages>
 int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C, int m, int n, int k, int slices,
                     int* fault_word, cudaStream_t stream) {
-  using S = GemmShape<BN, kStages, 1>;
+  using S = GemmShape<BN, kStages, 1, kModeSplitK>;
   GemmParams p = {};
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(k), S::kBM, S::kBK, true);
