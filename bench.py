@@ -133,6 +133,7 @@ def run_reference(args):
     from oracle import build_oracle
     build_oracle.build()
     import oracle
+    oracle.use_all_cores()
     rng = np.random.Generator(np.random.PCG64(SEED))
     budget = min(2.0, 150.0 / max(args.steps + args.warmup, 1))
     b = (rng.standard_normal((N, K), dtype=np.float32) * 0.1).astype(np.float16)
@@ -157,6 +158,28 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def reference_kernels(torch, a, b, c, ev_time):
+    """The reference's own kernels (its CuTe / CUTLASS sm80-era code, built unmodified for sm_100a by
+    baseline/build_reference.py) on the same inputs: comparison only."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not any(f.startswith("beam_C") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
+        return "not built"
+    try:
+        sys.path.insert(0, ref_dir)
+        import beam_C  # prints its cuBLAS / CUTLASS versions to stderr
+        res = {}
+        want = torch.matmul(a, b.t()).float()
+        for name in ("custom_gemmrc_128x128", "custom_gemmrc_128x256", "cutlass_gemmrc"):
+            fn = getattr(beam_C, name)
+            c.zero_()
+            ms = ev_time(lambda: fn(a, b, c), 5)
+            err = float((c.float() - want).abs().max() / want.abs().max())
+            res[name] = {"tflops": 2.0 * M_PER_GPU * N * K / ms * 1e-9, "max_abs_err_over_max": err}
+        return res
+    except Exception as ex:
+        return "failed: %r" % (ex,)
 
 
 def extras(beam, torch, a, b, c, peaks):
@@ -212,15 +235,22 @@ def extras(beam, torch, a, b, c, peaks):
         As = [(torch.rand(m, k, device="cuda") * 2 - 1).half() for _ in range(sets)]
         Bs = [(torch.rand(n, k, device="cuda") * 2 - 1).half() for _ in range(sets)]
         cc = torch.zeros(m, n, dtype=torch.float16, device="cuda")
-        us = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc)) for i in range(24)])
         bytes_ = 2.0 * (m * k + n * k + m * n)
+        # "overlapped": BEAM_FLAG_INPUTS_STABLE, i.e. consecutive calls may stream side by side (the inputs of a
+        # call are never the outputs of the call before it here); "plain": every call waits for the one before.
+        us_plain = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc))
+                             for i in range(24)])
+        us = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc, inputs_stable=True))
+                       for i in range(24)])
         gbs = bytes_ / (us * 1e-6) * 1e-9
         out["splitk_%dx%dx%d" % (m, n, k)] = {
-            "us": us, "algorithmic_bytes": bytes_, "GBps": gbs, "hbm_peak_GBps": peaks["hbm_gbs"],
-            "frac_of_%s_hbm" % peaks["source"]: gbs / peaks["hbm_gbs"],
+            "us_overlapped": us, "us_plain": us_plain, "algorithmic_bytes": bytes_, "GBps": gbs,
+            "hbm_peak_GBps": peaks["hbm_gbs"], "frac_of_%s_hbm" % peaks["source"]: gbs / peaks["hbm_gbs"],
+            "frac_plain": bytes_ / (us_plain * 1e-6) * 1e-9 / peaks["hbm_gbs"],
             "cublas_us": graph_us([(lambda i=i: torch.matmul(As[i % sets], Bs[i % sets].t(), out=cc))
                                    for i in range(24)])}
         del As, Bs
+    out["reference_kernels_sm80_on_b200"] = reference_kernels(torch, a, b, c, ev_time)
     m, n, k = 16384, 4096, 4096
     x = (torch.randn(m, k, device="cuda") * 0.02).half()
     w = (torch.randn(n, k, device="cuda") * 0.02).half()
@@ -342,6 +372,7 @@ def run_ours(args):
             from oracle import build_oracle
             build_oracle.build()
             import oracle
+            oracle.use_all_cores()
             tf, rows, dt = cpu_sample(oracle, ha.numpy(), hb.numpy(), 10.0)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                                     "sample": "first %d rows of A x all of B (%d x %d x %d), %.1f s" %
@@ -356,6 +387,42 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """A handful of launches of one kernel on its BASELINE shape, for `ncu ... python bench.py --profile X`.
+    layernorm runs a quarter of config 4's rows so that a full-set capture stays small."""
+    import torch
+    import beam
+    torch.cuda.set_device(0)
+    torch.manual_seed(SEED)
+    n_launch = max(args.steps, 1)
+    if args.profile == "gemm":
+        a = (torch.randn(M_PER_GPU, K, device="cuda") * 0.1).half()
+        b = (torch.randn(N, K, device="cuda") * 0.1).half()
+        c = torch.zeros(M_PER_GPU, N, dtype=torch.float16, device="cuda")
+        fn = lambda: beam.cutlass_gemmrc(a, b, c)
+    elif args.profile in ("splitk", "splitk64"):
+        m, n, k = (128, 256, 65536) if args.profile == "splitk" else (64, 64, 131072)
+        a = (torch.rand(m, k, device="cuda") * 2 - 1).half()
+        b = (torch.rand(n, k, device="cuda") * 2 - 1).half()
+        c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        fn = lambda: beam.cutlass_gemmrc_splitk(a, b, c, inputs_stable=True)
+    else:
+        m, n, k = 4096, 4096, 4096
+        a = (torch.randn(m, k, device="cuda") * 0.02).half()
+        b = (torch.randn(n, k, device="cuda") * 0.02).half()
+        g = (1 + 0.1 * torch.randn(n, device="cuda")).half()
+        bt = (0.1 * torch.randn(n, device="cuda")).half()
+        c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        fn = lambda: beam.cutlass_parallel_gemmrc_lnr(a, b, c, g, bt, 1e-5)
+    for _ in range(n_launch):
+        fn()
+    torch.cuda.synchronize()
+    st, word = beam.device_status()
+    print(json.dumps({"profile": args.profile, "launches": n_launch, "status": st, "fault_word": word}))
+    if st != 0:
+        raise SystemExit(1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -363,8 +430,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the cuBLAS / split-K / LayerNorm side measurements")
+    ap.add_argument("--profile", default=None, choices=["gemm", "splitk", "splitk64", "layernorm"],
+                    help="run a few launches of one kernel and exit (the command the ncu captures in profiles/ wrap)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -53,7 +53,7 @@ class beam_gemm_cfg(ctypes.Structure):
         ("split_k_slices", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
         ("l2_hints", ctypes.c_int),
-        ("reserved", ctypes.c_int * 1),
+        ("flags", ctypes.c_int),
     ]
 
 
@@ -84,6 +84,7 @@ def _load():
     L.beam_gemmrc_splitk_workspace_bytes.argtypes = [i, i, i, i, i]
     L.beam_gemmrc_splitk_heuristic.argtypes = [i, i, i, i]
     L.beam_cutlass_gemmrc_splitk.argtypes = [vp, vp, vp, i, i, i, i, vp, sz, vp]
+    L.beam_gemmrc_splitk_fp16.argtypes = [vp, vp, vp, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp, sz, vp]
     L.beam_cutlass_gemmrc_splitk_spec.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, vp, sz, vp]
     L.beam_gemmrc_layernorm_workspace_bytes.restype = sz
     L.beam_gemmrc_layernorm_workspace_bytes.argtypes = [i, i, i]
@@ -199,33 +200,41 @@ def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hi
         _raise(st, "beam_gemmrc_fp16")
 
 
-def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0):
-    """Split-K c = a @ b.T for small M, N and huge K; fp32 partials summed in slice order (bitwise
-    reproducible).  split_k_slices = 0 lets the library choose (slot of cutlass_gemmrc_splitk.cu:59-105)."""
+FLAG_INPUTS_STABLE = 1
+
+
+def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable):
     m, n, k = _check_abc(a, b, c)
     L = _load()
+    cfg = beam_gemm_cfg(int(tile_n), 0, 0, 0, int(split_k_slices), 0, 0, FLAG_INPUTS_STABLE if inputs_stable else 0)
     with torch.cuda.device(a.device):
-        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, 0, int(split_k_slices))
+        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, int(tile_n), int(split_k_slices))
+        if nbytes > (4 << 30):
+            raise ValueError("split-K scratch of %d bytes: split-K is meant for small M*N" % nbytes)
         ws = _workspace(a.device, nbytes)
-        st = L.beam_cutlass_gemmrc_splitk(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, int(split_k_slices),
-                                          ws.data_ptr(), ws.numel(), _stream(a))
+        st = L.beam_gemmrc_splitk_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg),
+                                       ws.data_ptr(), ws.numel(), _stream(a))
     if st != BEAM_OK:
-        _raise(st, "beam_cutlass_gemmrc_splitk")
+        _raise(st, "beam_gemmrc_splitk_fp16")
 
 
-def cutlass_gemmrc_splitk_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64], split_k_slices=0):
-    """Split-K with the tile's N taken from shape_threadblock[1] (64, 128 or 256)."""
-    m, n, k = _check_abc(a, b, c)
+def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0, inputs_stable=False):
+    """Split-K c = a @ b.T for small M, N and huge K; fp32 partials summed in a fixed order (bitwise
+    reproducible).  split_k_slices = 0 lets the library choose (slot of cutlass_gemmrc_splitk.cu:59-105).
+    inputs_stable=True promises that a and b are not outputs of the kernel just before this call on the
+    stream, which lets back-to-back calls overlap (BEAM_FLAG_INPUTS_STABLE)."""
+    _splitk(a, b, c, 0, split_k_slices, inputs_stable)
+
+
+def cutlass_gemmrc_splitk_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64], split_k_slices=0,
+                               inputs_stable=False):
+    """Split-K with the tile's N taken from shape_threadblock[1] (64, 128 or 256); shape_warp is accepted for
+    signature compatibility (cuda/cutlass_kernels/main.cc:137-141) and ignored."""
     tbm, tbn = _pair(shape_threadblock, "shape_threadblock")
-    wm, wn = _pair(shape_warp, "shape_warp")
-    L = _load()
-    with torch.cuda.device(a.device):
-        nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, tbn, int(split_k_slices))
-        ws = _workspace(a.device, nbytes)
-        st = L.beam_cutlass_gemmrc_splitk_spec(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, tbm, tbn, wm, wn,
-                                               int(split_k_slices), ws.data_ptr(), ws.numel(), _stream(a))
-    if st != BEAM_OK:
-        _raise(st, "beam_cutlass_gemmrc_splitk_spec")
+    _pair(shape_warp, "shape_warp")
+    if tbn not in (64, 128, 256):
+        raise ValueError("shape_threadblock[1] must be 64, 128 or 256")
+    _splitk(a, b, c, tbn, split_k_slices, inputs_stable)
 
 
 def cutlass_parallel_gemmrc_lnr(a, b, c, gamma, beta, eps=1e-5):

@@ -27,6 +27,7 @@ struct ExtraArgs {
   float eps = 0.f;
   int slices = 1;
   int l2_hints = 0;
+  int flags = 0;
   float2* row_part = nullptr;
   int* tickets = nullptr;
   int* ln_queue = nullptr;
@@ -101,6 +102,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.slices = ex.slices;
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
+  p.flags = ex.flags;
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
   p.trace = g_trace_buffer;
@@ -187,12 +189,16 @@ int splitk_tile_n(int n, int tile_n) {
   return n <= 64 ? 64 : 128;
 }
 
-// One work item per SM: slices = SMs / tiles, but never fewer than 4 k-blocks (256 of K) per slice,
-// so that the fill of the TMA ring is amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:
-// 44-57, targets the 108 SMs of an A100 and rounds to half waves.)
-int splitk_heuristic(int m, int n, int k, int tile_n) {
+// Plain calls: one work item per SM (slices = SMs / tiles), but never fewer than 4 k-blocks (256 of K) per
+// slice, so that the fill of the TMA ring is amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:44-57,
+// targets the 108 SMs of an A100 and rounds to half waves.)
+// Calls that carry BEAM_FLAG_INPUTS_STABLE overlap with their neighbours on the stream, so the grid is sized by
+// bytes instead: about 650 KB of operand traffic per CTA, which leaves room for two or three consecutive calls
+// to stream side by side (measured optimum on B200 for 128x256x65536 and 64x64x131072).
+int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
   const int bn = splitk_tile_n(n, tile_n);
-  const long long tiles = static_cast<long long>((m + 127) / 128) * ((n + bn - 1) / bn);
+  const long long m_tiles = (m + 127) / 128, n_tiles = (n + bn - 1) / bn;
+  const long long tiles = m_tiles * n_tiles;
   const int num_kb = (k + 63) / 64;
   int sms = 148;
   int err = 0;
@@ -203,6 +209,12 @@ int splitk_heuristic(int m, int n, int k, int tile_n) {
     (void)cudaGetLastError();
   }
   long long s = sms / (tiles > 0 ? tiles : 1);
+  if (flags & BEAM_FLAG_INPUTS_STABLE) {
+    // every N tile re-reads its rows of A, every M tile its rows of B (from L2 after the first reader)
+    const double bytes = 2.0 * k * (static_cast<double>(m) * n_tiles + static_cast<double>(n) * m_tiles);
+    const long long by_bytes = static_cast<long long>(bytes / (650.0 * 1024.0) / static_cast<double>(tiles) + 0.5);
+    if (by_bytes < s) s = by_bytes;
+  }
   const long long cap = num_kb / 4 > 0 ? num_kb / 4 : 1;
   if (s > cap) s = cap;
   if (s > 256) s = 256;
@@ -210,20 +222,21 @@ int splitk_heuristic(int m, int n, int k, int tile_n) {
   return static_cast<int>(s);
 }
 
-int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested) {
+int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested, int flags) {
   const int num_kb = (k + 63) / 64;
   if (requested > 0 && requested <= num_kb && requested <= 1024) return requested;
-  return splitk_heuristic(m, n, k, tile_n);
+  return splitk_heuristic(m, n, k, tile_n, flags);
 }
 
 size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  const int s = splitk_resolve_slices(m, n, k, tile_n, slices);
+  // sized for the plain heuristic, which never picks fewer slices than the overlapped one
+  const int s = splitk_resolve_slices(m, n, k, tile_n, slices, 0);
   return static_cast<size_t>(s) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
 }
 
 int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, int tile_n, int slices,
-                  void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                  void* workspace, size_t workspace_bytes, cudaStream_t stream, int flags) {
   int st = validate_gemm_args(A, B, C, m, n, k);
   if (st != BEAM_OK) return st;
   if (slices < 0) return BEAM_ERR_INVALID_ARG;
@@ -231,7 +244,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
   const int bn = splitk_tile_n(n, tile_n);
-  const int s = splitk_resolve_slices(m, n, k, bn, slices);
+  const int s = splitk_resolve_slices(m, n, k, bn, slices, flags);
   const size_t need = static_cast<size_t>(s) * m * n * sizeof(float);
   if (!workspace || workspace_bytes < need) return BEAM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
@@ -239,6 +252,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   ExtraArgs ex;
   ex.scratch = static_cast<float*>(workspace);
   ex.slices = s;
+  ex.flags = flags;
   if (bn == 64)
     st = launch_instance<64, 8, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
   else if (bn == 128)

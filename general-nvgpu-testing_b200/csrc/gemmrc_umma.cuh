@@ -59,6 +59,7 @@ struct GemmParams {
   int slices;   // split-K slices (1 otherwise)
   int hint_a;   // L2 eviction policy of the A loads: 0 normal, 1 evict-first, 2 evict-last
   int hint_b;   // same for the B loads
+  int flags;    // BEAM_FLAG_* bits of the call
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
@@ -368,7 +369,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     if constexpr (kMode == kModeSplitK) {
       // Launched as a programmatic dependent of the previous call's reduction: everything above may run
       // while that grid drains; nothing below reads or writes global memory before it has completed.
-      ptx::grid_dependency_wait();
+      // With BEAM_FLAG_INPUTS_STABLE the caller vouches that A and B are not that grid's outputs, and the
+      // loads below may start at once; the partial stores wait for it in the epilogue either way.
+      if (!(p.flags & 1)) ptx::grid_dependency_wait();
       // In turn, let this call's reduction kernel become resident early; it blocks until this grid is done.
       ptx::grid_launch_dependents();
     }

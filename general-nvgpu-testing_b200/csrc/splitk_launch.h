@@ -7,10 +7,10 @@ namespace beam {
 
 // tile_n = 0 picks the tile from N; slices = 0 picks the split factor from the SM count.
 int splitk_tile_n(int n, int tile_n);
-int splitk_heuristic(int m, int n, int k, int tile_n);
-int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested);
+int splitk_heuristic(int m, int n, int k, int tile_n, int flags = 0);
+int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested, int flags = 0);
 size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices);
 int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, int tile_n, int slices,
-                  void* workspace, size_t workspace_bytes, cudaStream_t stream);
+                  void* workspace, size_t workspace_bytes, cudaStream_t stream, int flags = 0);
 
 }  // namespace beam

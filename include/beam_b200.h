@@ -56,8 +56,15 @@ typedef struct beam_gemm_cfg {
   int max_ctas;       /* cap on the persistent grid (0 = all SMs)                              */
   int l2_hints;       /* L2 eviction policy of the TMA loads, two decimal digits: tens = A, ones = B;
                          0 normal, 1 evict-first, 2 evict-last (e.g. 21 = keep A, stream B)          */
-  int reserved[1];
+  int flags;          /* BEAM_FLAG_* bits                                                       */
 } beam_gemm_cfg;
+
+/* Split-K only.  The caller guarantees that A and B are not outputs of the kernel that immediately precedes
+ * this call on the stream (they were complete before that kernel started).  The first kernel of the call is
+ * a programmatic dependent launch; with this flag it starts streaming A and B while the preceding kernel
+ * (typically the previous split-K call's reduction) is still finishing, and only its writes wait for that
+ * kernel to complete.  Without the flag it waits before its first global read, which is always safe. */
+#define BEAM_FLAG_INPUTS_STABLE 1
 
 BEAM_API const char* beam_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
@@ -109,6 +116,12 @@ BEAM_API size_t beam_gemmrc_splitk_workspace_bytes(int m, int n, int k, int tile
  * least 256 of K per slice.  Replaces get_slice_heuristic (cuda/cutlass_kernels/
  * cutlass_gemmrc_splitk.cu:44-57), which models the 108 SMs of an A100. */
 BEAM_API int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n);
+
+/* Generic split-K entry: cfg->tile_n (0 = default), cfg->split_k_slices (0 = heuristic) and cfg->flags
+ * (BEAM_FLAG_INPUTS_STABLE) are honoured; cfg may be NULL.  The two registry names below are presets. */
+BEAM_API int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n, int k,
+                                     const beam_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
+                                     void* stream);
 
 /* Registry name `cutlass_gemmrc_splitk` — replaces entry_cutlass_gemmrc_splitk (cuda/cutlass_kernels/
  * cutlass_gemmrc_splitk.cu:59-105).  K is cut into `split_k_slices` contiguous runs of 64-wide

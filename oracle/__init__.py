@@ -33,6 +33,7 @@ def lib():
         L.oracle_half_to_float.argtypes = [ctypes.c_uint16]
         L.oracle_half_to_float.restype = f
         L.oracle_num_threads.restype = i
+        L.oracle_set_num_threads.argtypes = [i]
         _LIB = L
     return _LIB
 
@@ -55,6 +56,16 @@ def _check(st, what):
 
 def num_threads():
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores():
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says; returns the thread count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(n)
+    return num_threads()
 
 
 def gemmrc(a, b):
