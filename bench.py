@@ -203,7 +203,7 @@ def extras(beam, torch, a, b, c, peaks):
     ms = ev_time(lambda: torch.matmul(a, b.t(), out=c), 20)
     out["cublas_fp32acc_tflops"] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
     for name, tb in (("128x128", [128, 128]), ("128x256", [128, 256]), ("256x128", [256, 128]),
-                     ("256x256", [256, 256])):
+                     ("256x256", [256, 256]), ("256x512", [256, 512])):
         ms = ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb), 10)
         out["tile_%s_tflops" % name] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
 
@@ -352,8 +352,8 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "f16 in, f32 accumulate, f16 out", "data": "synthetic",
             "config": {"workload": "fp16 gemmrc M=%d N=%d K=%d (BASELINE configs[1] per GPU; row-sharded "
                                    "configs[4] at 8 GPUs)" % (M_PER_GPU * world, N, K),
-                       "rows_per_gpu": M_PER_GPU, "kernel": "cutlass_gemmrc: 256x256 tile, cta_group::2, 6-stage TMA "
-                       "ring, TMA-store epilogue", "parallelism": "rows of A sharded x%d, B replicated, no collective" % world,
+                       "rows_per_gpu": M_PER_GPU, "kernel": "cutlass_gemmrc: 256x512 tile per CTA pair (cta_group::2, two N=256 "
+                       "accumulators), 4-stage TMA ring, TMA-store epilogue", "parallelism": "rows of A sharded x%d, B replicated, no collective" % world,
                        "l2": "A, B, C are 3 x 128 MiB per GPU, larger than the 126 MB L2; no flush between steps"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * (M_PER_GPU * K + N * K) * world,
                     "d2h_bytes_per_step": 2 * M_PER_GPU * N * world, "steps": e2e_steps, "matches_device_path": e2e_ok,

@@ -101,6 +101,7 @@ class OperatorTuner:
     def _get_gemm_specs(self) -> List[Operator]:
         """Large-GEMM candidates: (tile N, CTAs per tile, ring depth)."""
         search_space = [
+            (512, 2, 4), (512, 2, 3),
             (256, 2, 4), (256, 2, 5), (256, 2, 6),
             (128, 2, 6), (128, 2, 8),
             (256, 1, 3), (256, 1, 4),
@@ -108,7 +109,7 @@ class OperatorTuner:
         ]
         ret = [Operator(partial(_C.gemmrc, tile_n=tn, cta_pair=cp, stages=st)) for tn, cp, st in search_space]
         # The reference's own spelling of the tile families (tuner.py:52-59) stays valid.
-        for tb in ([128, 128], [128, 256], [256, 128], [256, 256]):
+        for tb in ([128, 128], [128, 256], [256, 128], [256, 256], [256, 512]):
             ret.append(Operator(partial(_C.cutlass_gemmrc_spec, shape_threadblock=tb, shape_warp=[64, 64])))
         return ret
 

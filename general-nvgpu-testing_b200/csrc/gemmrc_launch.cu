@@ -3,6 +3,7 @@
 #include "gemmrc_launch.h"
 
 #include "gemmrc_umma.cuh"
+#include "gemmrc_wide.cuh"
 #include "layernorm_launch.h"
 #include "splitk_launch.h"
 
@@ -28,6 +29,8 @@ struct ExtraArgs {
   int slices = 1;
   int l2_hints = 0;
   int flags = 0;
+  int raster = 0;
+  int k_phases = 0;
   float2* row_part = nullptr;
   int* tickets = nullptr;
   int* ln_queue = nullptr;
@@ -102,7 +105,14 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.slices = ex.slices;
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
+  p.hint_c = (ex.l2_hints / 100) % 10;
   p.flags = ex.flags;
+  {
+    int ph = ex.k_phases > 0 ? ex.k_phases : 1;
+    const int num_kb = (k + S::kBK - 1) / S::kBK;
+    while (ph > 1 && (ph > num_kb || (ph & (ph - 1)) != 0)) ph >>= 1;  // a power of two, at most one offset per k-block
+    p.k_phases = ph < 1 ? 1 : ph;
+  }
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
   p.trace = g_trace_buffer;
@@ -133,7 +143,71 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;
   }
+  // The split raster indexes workers by SM id: only valid when the grid fills the device, one CTA per SM.
+  p.raster = (ex.raster == 1 && clusters * kCta == ctx->sm_count && p.m_tiles >= 2) ? 1 : 0;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
+  return BEAM_OK;
+}
+
+// 256 x 512 tiles on CTA pairs (gemmrc_wide.cuh).
+template <int kStages>
+int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
+                         int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
+  using S = WideShape<kStages>;
+  auto kernel = gemmrc_wide_kernel<kStages>;
+  static int configured_clusters[64] = {0};
+  int& resident = configured_clusters[ctx->device];
+  if (resident == 0) {
+    if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
+    BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
+                  "cudaFuncSetAttribute(smem)");
+    resident = ctx->sm_count / 2 > 0 ? ctx->sm_count / 2 : 1;
+  }
+  GemmParams p = {};
+  int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                          static_cast<uint64_t>(k), S::kBM, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                      S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n), 32,
+                      64, true);
+  if (st != BEAM_OK) return st;
+  p.c = static_cast<__half*>(C);
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ldc = n;
+  p.m_tiles = (m + 255) / 256;
+  p.n_tiles = (n + S::kTileN - 1) / S::kTileN;
+  p.group_m = group_m > 0 ? group_m : 12;
+  p.slices = 1;
+  p.hint_a = (ex.l2_hints / 10) % 10;
+  p.hint_b = ex.l2_hints % 10;
+  p.hint_c = (ex.l2_hints / 100) % 10;
+  p.k_phases = 1;
+  p.status = ctx->status_word;
+#ifdef BEAM_TRACE
+  p.trace = nullptr;
+  p.debug = 0;
+#endif
+  const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  int clusters = resident;
+  if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (items < clusters) clusters = static_cast<int>(items);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * 2), 1, 1);
+  cfg.blockDim = dim3(S::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_wide)");
   return BEAM_OK;
 }
 
@@ -167,6 +241,16 @@ int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, co
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ExtraArgs ex;
   ex.l2_hints = plan.l2_hints;
+  ex.raster = plan.raster;
+  ex.k_phases = plan.k_phases;
+  if (plan.tile_n == 512) {
+    if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
+    if (plan.stages == 0 || plan.stages == 4)
+      return launch_wide_instance<4>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+    if (plan.stages == 3)
+      return launch_wide_instance<3>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+    return BEAM_ERR_UNSUPPORTED;
+  }
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
   BEAM_GEMM_CASE(256, 6, 2)

@@ -59,7 +59,10 @@ struct GemmParams {
   int slices;   // split-K slices (1 otherwise)
   int hint_a;   // L2 eviction policy of the A loads: 0 normal, 1 evict-first, 2 evict-last
   int hint_b;   // same for the B loads
+  int hint_c;   // same for the C stores (GEMM mode)
   int flags;    // BEAM_FLAG_* bits of the call
+  int raster;   // GEMM: 0 = one grouped walk over all tiles; 1 = the two halves of the SM id space split M
+  int k_phases; // GEMM, LayerNorm: number of distinct K-loop starting offsets (power of two, >= 1)
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
@@ -130,21 +133,27 @@ struct WorkItem {
 //              in flight together share A rows and B rows in L2 (the reference's CTA remap at
 //              cute_gemm_128x128.cu:23-33, restated for a persistent grid).
 //   split-K:   items are (tile, slice), slice fastest; k-blocks are dealt out as evenly as possible.
+// How one CTA (pair) walks the work: item j is `first + j * stride` within the M-tile range
+// [m_base, m_base + m_count) (the whole problem unless the raster splits it between the two halves of the chip).
+struct Walk {
+  int first, stride, m_base, m_count;
+};
+
 template <int kMode>
-__device__ __forceinline__ bool work_item(const GemmParams& p, int first, int stride, int j, int num_kb,
-                                          WorkItem& w) {
+__device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk, int j, int num_kb, WorkItem& w) {
+  const int first = walk.first, stride = walk.stride;
   w.slice = 0;
   w.kb0 = 0;
   w.kb1 = num_kb;
   if constexpr (kMode != kModeSplitK) {
     const int t = first + j * stride;
-    if (t >= p.m_tiles * p.n_tiles) return false;
+    if (t >= walk.m_count * p.n_tiles) return false;
     const int per_group = p.group_m * p.n_tiles;
     const int g = t / per_group;
     const int first_m = g * p.group_m;
-    const int rows = min(p.group_m, p.m_tiles - first_m);
+    const int rows = min(p.group_m, walk.m_count - first_m);
     const int r = t - g * per_group;
-    w.mt = first_m + r % rows;
+    w.mt = walk.m_base + first_m + r % rows;
     w.nt = r / rows;
     return true;
   } else {
@@ -327,10 +336,41 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (threadIdx.x == 0) BEAM_STAMP(0);
+#ifdef BEAM_TRACE
+  if (threadIdx.x == 0 && p.trace) {
+    uint32_t smid, nsmid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    asm volatile("mov.u32 %0, %%nsmid;" : "=r"(nsmid));
+    p.trace[static_cast<size_t>(blockIdx.x) * 16 + 15] = (static_cast<unsigned long long>(nsmid) << 32) | smid;
+  }
+#endif
   const uint32_t cta_rank = (kCta == 2) ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
-  const int stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int first = (kCta == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  Walk walk;
+  walk.stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  walk.first = (kCta == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  walk.m_base = 0;
+  walk.m_count = p.m_tiles;
+  if constexpr (kMode == kModeGemm) {
+    if (p.raster == 1) {
+      // Split raster: the SMs with the lower half of the SM ids take the upper half of the M tiles' rows...
+      // each half of the chip then touches only its own rows of A, so those lines are cached once, not in
+      // both halves of the L2.  One CTA per SM and a grid that fills the device (checked by the launcher)
+      // make SM id / kCta a dense worker index; a pair sits on SMs (2t, 2t + 1).
+      uint32_t smid, nsmid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      asm volatile("mov.u32 %0, %%nsmid;" : "=r"(nsmid));
+      const int workers = static_cast<int>(nsmid) / kCta;
+      const int v = static_cast<int>(smid) / kCta;
+      const int half = workers / 2;
+      const int upper = v >= half ? 1 : 0;
+      walk.first = v - upper * half;
+      walk.stride = upper ? workers - half : half;
+      const int m_half = p.m_tiles / 2;
+      walk.m_base = upper ? m_half : 0;
+      walk.m_count = upper ? p.m_tiles - m_half : m_half;
+    }
+  }
 
   // ---- shared-memory carve-up (tile buffers need 1024-byte alignment for the 128 B swizzle)
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -379,10 +419,14 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // The ring starts empty, so the first loads need no wait: put them in flight before the CTA-wide
       // set-up barrier (TMEM allocation) instead of after it.  Thread 0 is also the producer thread.
       WorkItem w0;
-      if (work_item<kMode>(p, first, stride, 0, num_kb, w0)) {
+      if (work_item<kMode>(p, walk, 0, num_kb, w0)) {
         const int row_a = w0.mt * S::kBM;
         const int row_b = w0.nt * BN;
-        for (int kb = w0.kb0; kb < w0.kb1 && preloaded < static_cast<uint32_t>(kStages); ++kb, ++preloaded) {
+        const int nkb0 = w0.kb1 - w0.kb0;
+        const int rot0 = (kMode == kModeSplitK) ? 0 : ((w0.mt + w0.nt) & (p.k_phases - 1)) * (nkb0 / p.k_phases);
+        for (; static_cast<int>(preloaded) < nkb0 && preloaded < static_cast<uint32_t>(kStages); ++preloaded) {
+          const int i0 = static_cast<int>(preloaded);
+          const int kb = w0.kb0 + (i0 + rot0 < nkb0 ? i0 + rot0 : i0 + rot0 - nkb0);
           const int s = static_cast<int>(preloaded);
           ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
           ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, ptx::l2_policy(p.hint_a));
@@ -411,7 +455,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       WorkItem w;
-      for (int j = 0; alive && work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
+      for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
         int row_a = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
         int row_b = w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
 #ifdef BEAM_TRACE
@@ -420,12 +464,18 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           row_b = static_cast<int>(cta_rank) * S::kBRows;
         }
 #endif
-        int kb = w.kb0;
+        // Rotated K loop: tile (mt, nt) starts at k-block rot and wraps.  Tiles that share rows of A (same mt)
+        // or of B (same nt) start at different offsets, so a shared line is touched every 1/k_phases of a
+        // wave instead of once per wave, close enough together to still be in L2 the next time.
+        const int nkb = w.kb1 - w.kb0;
+        const int rot = (kMode == kModeSplitK) ? 0 : ((w.mt + w.nt) & (p.k_phases - 1)) * (nkb / p.k_phases);
+        int i = 0;
         if (j == 0) {  // these are already in flight
-          kb += static_cast<int>(preloaded);
+          i = static_cast<int>(preloaded);
           it = preloaded;
         }
-        for (; kb < w.kb1; ++kb, ++it) {
+        for (; i < nkb; ++i, ++it) {
+          const int kb = w.kb0 + (i + rot < nkb ? i + rot : i + rot - nkb);
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {
@@ -453,7 +503,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       uint32_t it = 0;
       bool alive = true;
       WorkItem w;
-      for (int j = 0; alive && work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
+      for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;
         const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
         {
@@ -511,7 +561,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     uint32_t ln_ring_count = 0;                        // LayerNorm: boxes this warp's landing ring has received
     const uint32_t ln_bufs = staging_base + quad * S::kBufsPerWarp * S::kStoreBufBytes;
     WorkItem w;
-    for (int j = 0; work_item<kMode>(p, first, stride, j, num_kb, w); ++j) {
+    for (int j = 0; work_item<kMode>(p, walk, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
       const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
       // Lane 0 polls (with back-off) for the whole warp, which stays converged for the .sync.aligned TMEM
@@ -627,7 +677,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           __syncwarp();
           if (lane == 0) {
             if constexpr (kMode == kModeGemm)
-              ptx::tma_store_2d(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
+              ptx::tma_store_2d_hint(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32,
+                                     ptx::l2_policy(p.hint_c));
             else
               ptx::tma_store_3d(&p.tm_s, buf, col0 + c, row0 + static_cast<int>(quad) * 32, w.slice);
             ptx::tma_store_commit();

@@ -1,0 +1,242 @@
+// 256 x 512 output tile per CTA pair: the large-GEMM kernel with both TMEM accumulators live at once.
+//
+// Same roles, barriers and TMA-store epilogue as gemmrc_umma_kernel in pair mode, but a k-block stage holds
+// A (128 rows per CTA) and TWO B boxes (128 rows per CTA each, the two 256-column halves of the tile), and the
+// leader issues tcgen05.mma (M = 256, N = 256) for both halves against the same A.  Per unit of math this
+// moves 24 KB instead of 32 KB per CTA through L2 and shared memory, and a wave of 74 tiles touches fewer
+// distinct operand rows per flop.
+//
+// The price: TMEM (512 columns) holds one tile, so the epilogue cannot hide behind the next tile's main loop
+// by double-buffering.  It hides behind the start of it instead: the first `kStages` k-blocks of a tile are
+// issued half-major (all of half 0, then all of half 1), so the issuer only needs half 0 drained to start
+// and half 1 is drained meanwhile.
+#pragma once
+
+#include "gemmrc_umma.cuh"
+
+namespace beam {
+
+template <int kStages>
+struct WideShape {
+  static constexpr int kBM = 128;
+  static constexpr int kBK = 64;
+  static constexpr int kHalfN = 256;
+  static constexpr int kTileN = 512;
+  static constexpr int kBRows = kHalfN / 2;  // rows of one B half that one CTA of the pair loads
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBHalfBytes = kBRows * kBK * 2;
+  static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kStoreBufBytes = 32 * 128;
+  static constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;
+  static constexpr int kThreads = 192;
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
+  static_assert((2 * kStages + 3) * 8 + 16 <= kBarBytes, "barrier block too small");
+};
+
+template <int kStages>
+__global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_constant__ GemmParams p) {
+  using S = WideShape<kStages>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  Walk walk;
+  walk.stride = static_cast<int>(gridDim.x >> 1);
+  walk.first = static_cast<int>(blockIdx.x >> 1);
+  walk.m_base = 0;
+  walk.m_count = p.m_tiles;
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t staging_base = smem_base + kStages * S::kStageBytes;
+  const uint32_t bar_base = staging_base + S::kStagingBytes;
+  auto smem_a = [&](int s) { return smem_base + s * S::kStageBytes; };
+  auto smem_b = [&](int s, int h) { return smem_base + s * S::kStageBytes + S::kABytes + h * S::kBHalfBytes; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  const uint32_t tmem_full_bar = bar_base + 8u * (2 * kStages);
+  auto tmem_empty_bar = [&](int h) { return bar_base + 8u * (2 * kStages + 1 + h); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 3));
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    ptx::mbar_init(tmem_full_bar, 1);
+    ptx::mbar_init(tmem_empty_bar(0), 8);  // one arrive per epilogue warp of each CTA
+    ptx::mbar_init(tmem_empty_bar(1), 8);
+    *cta_abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&p.tm_a);
+    ptx::prefetch_tensormap(&p.tm_b);
+    ptx::prefetch_tensormap(&p.tm_c);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<2>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
+    ptx::tmem_relinquish<2>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (p.k + S::kBK - 1) / S::kBK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      const uint64_t pol_a = ptx::l2_policy(p.hint_a);
+      const uint64_t pol_b = ptx::l2_policy(p.hint_b);
+      WorkItem w;
+      for (int j = 0; alive && work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
+        const int row_a = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
+        const int row_b0 = w.nt * S::kTileN + static_cast<int>(cta_rank) * S::kBRows;
+        const int row_b1 = row_b0 + S::kHalfN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {
+            alive = false;
+            break;
+          }
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
+          const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
+          ptx::tma_load_2d_pair_hint(smem_a(s), &p.tm_a, lead_bar, kb * S::kBK, row_a, pol_a);
+          ptx::tma_load_2d_pair_hint(smem_b(s, 0), &p.tm_b, lead_bar, kb * S::kBK, row_b0, pol_b);
+          ptx::tma_load_2d_pair_hint(smem_b(s, 1), &p.tm_b, lead_bar, kb * S::kBK, row_b1, pol_b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kHalfN);
+      uint32_t it = 0;
+      bool alive = true;
+      WorkItem w;
+      auto issue_half = [&](int s, int h, bool first_kb) {
+        const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s));
+        const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s, h));
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(h) * S::kHalfN;
+#pragma unroll
+        for (int kk = 0; kk < S::kBK / 16; ++kk)
+          ptx::umma_f16<2>(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, (!first_kb || kk > 0) ? 1u : 0u);
+      };
+      for (int j = 0; alive && work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
+        const uint32_t tile_ph = static_cast<uint32_t>(j) & 1u;
+        const int lead_in = num_kb < kStages ? num_kb : kStages;  // k-blocks issued half-major
+        // half 0 of the first k-blocks: needs only half 0 of the previous tile drained
+        if (!bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        ptx::tc_fence_after();
+        for (int g = 0; g < lead_in && alive; ++g) {
+          const uint32_t k = it + static_cast<uint32_t>(g);
+          const int s = k % kStages;
+          if (!bounded_wait(full_bar(s), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          issue_half(s, 0, g == 0);
+        }
+        if (!alive) break;
+        // half 1 of the same k-blocks; their stages are released here
+        if (!bounded_wait(tmem_empty_bar(1), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        ptx::tc_fence_after();
+        for (int g = 0; g < lead_in; ++g) {
+          const int s = (it + static_cast<uint32_t>(g)) % kStages;
+          issue_half(s, 1, g == 0);
+          ptx::umma_commit_pair_both(empty_bar(s), 0x3);
+        }
+        it += static_cast<uint32_t>(lead_in);
+        for (int kb = lead_in; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!bounded_wait(full_bar(s), (it / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          issue_half(s, 0, false);
+          issue_half(s, 1, false);
+          ptx::umma_commit_pair_both(empty_bar(s), 0x3);
+        }
+        if (alive) ptx::umma_commit_pair_both(tmem_full_bar, 0x3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const uint32_t quad = warp & 3u;
+    const uint32_t lead_empty0 = ptx::mapa(tmem_empty_bar(0), 0);
+    uint32_t store_count = 0;
+    WorkItem w;
+    for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
+      if (!bounded_wait_warp(tmem_full_bar, static_cast<uint32_t>(j) & 1u, cta_abort, p.status, kFaultEpilogueWait,
+                             lane))
+        break;
+      ptx::tc_fence_after();
+      const int row0 = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const int col0 = w.nt * S::kTileN + h * S::kHalfN;
+        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + static_cast<uint32_t>(h) * S::kHalfN;
+#pragma unroll 1
+        for (int c = 0; c < S::kHalfN; c += 64) {
+          uint32_t v0[32], v1[32], out[32];
+          ptx::tmem_ld_32x32(taddr + c, v0);
+          ptx::tmem_ld_32x32(taddr + c + 32, v1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            out[q] = ptx::pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
+            out[16 + q] = ptx::pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+          }
+          if (col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m) {
+            const uint32_t buf = staging_base + (quad * 2u + (store_count & 1u)) * S::kStoreBufBytes;
+            if (store_count >= 2) {
+              if (lane == 0) ptx::tma_store_wait_read<1>();
+              __syncwarp();
+            }
+            const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), out[4 * jj],
+                                out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d_hint(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32,
+                                     ptx::l2_policy(p.hint_c));
+              ptx::tma_store_commit();
+            }
+            ++store_count;
+          }
+        }
+        // this half of the accumulator is drained: the issuer may overwrite it
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * static_cast<uint32_t>(h));
+      }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+  __syncwarp();
+  if (*cta_abort) abort_drain_delay();
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<2>(tmem_base, S::kTmemCols);
+  }
+}
+
+}  // namespace beam

@@ -48,15 +48,20 @@ extern "C" {
  * reference's shape_threadblock / shape_warp vectors (cuda/cutlass_kernels/main.cc:129-141) in
  * the auto-tuner's search space. */
 typedef struct beam_gemm_cfg {
-  int tile_n;         /* UMMA N per output tile: 64, 128 or 256                               */
+  int tile_n;         /* output tile N: 64, 128, 256, or 512 (two UMMA N = 256 halves, pair only)   */
   int cta_pair;       /* 1 = one CTA per 128-row tile; 2 = cta_group::2 pair on a 256-row tile */
   int stages;         /* depth of the TMA->UMMA shared-memory ring (2..8)                      */
   int group_m;        /* tile rasterisation: M-tiles per L2 group                              */
   int split_k_slices; /* split-K only: number of K slices (0 = heuristic)                      */
   int max_ctas;       /* cap on the persistent grid (0 = all SMs)                              */
-  int l2_hints;       /* L2 eviction policy of the TMA loads, two decimal digits: tens = A, ones = B;
-                         0 normal, 1 evict-first, 2 evict-last (e.g. 21 = keep A, stream B)          */
+  int l2_hints;       /* L2 eviction policy, three decimal digits: hundreds = C stores, tens = A loads,
+                         ones = B loads; 0 normal, 1 evict-first, 2 evict-last                      */
   int flags;          /* BEAM_FLAG_* bits                                                       */
+  int raster;         /* large GEMM: 0 one grouped walk over all tiles; 1 the two halves of the SM id
+                         space each take half of the M tiles                                     */
+  int k_phases;       /* large GEMM: tiles start their K loop at one of this many evenly spaced
+                         offsets (1, 2, 4 or 8), chosen by (m_tile + n_tile).  A tuning knob: on B200
+                         anything but 1 (the default, also for 0) raises DRAM traffic.             */
 } beam_gemm_cfg;
 
 /* Split-K only.  The caller guarantees that A and B are not outputs of the kernel that immediately precedes
@@ -94,12 +99,13 @@ BEAM_API int beam_custom_gemmrc_128x128(const void* A, const void* B, void* C, i
 BEAM_API int beam_custom_gemmrc_128x256(const void* A, const void* B, void* C, int m, int n, int k, void* stream);
 
 /* Registry name `cutlass_gemmrc` — replaces entry_cutlass_gemmrc (cuda/cutlass_kernels/
- * cutlass_gemmrc.cu:21-40): the library's best default, a 256x256 tile on a CTA pair. */
+ * cutlass_gemmrc.cu:21-40): the library's best default: CTA pairs on 256x512 tiles when the problem has
+ * at least four waves of them, 256x256 tiles otherwise. */
 BEAM_API int beam_cutlass_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, void* stream);
 
 /* Registry name `cutlass_gemmrc_spec` — replaces entry_cutlass_gemmrc_spec (cuda/cutlass_kernels/
  * cutlass_gemmrc.cu:55-111).  shape_threadblock = {tb_m, tb_n} selects the tile family:
- * {128,128}, {128,256} -> one CTA per tile; {256,128}, {256,256} -> CTA pair.  shape_warp is accepted
+ * {128,128}, {128,256} -> one CTA per tile; {256,128}, {256,256}, {256,512} -> CTA pair.  shape_warp is accepted
  * for signature compatibility and ignored (a UMMA has no warp tile).  Unlike the reference, an
  * unknown shape returns BEAM_ERR_UNSUPPORTED instead of silently doing nothing (:73-80). */
 BEAM_API int beam_cutlass_gemmrc_spec(const void* A, const void* B, void* C, int m, int n, int k, int tb_m, int tb_n,

@@ -60,7 +60,7 @@ def test_config1_plumbing_512_cubed(beam, oracle_mod, name):
     assert oracle_mod.max_abs_over_max(c.cpu().numpy(), want) <= 2e-3
 
 
-@pytest.mark.parametrize("tb", [[128, 128], [128, 256], [256, 128], [256, 256]])
+@pytest.mark.parametrize("tb", [[128, 128], [128, 256], [256, 128], [256, 256], [256, 512]])
 def test_spec_tile_families(beam, oracle_mod, tb):
     a, b = _inputs(768, 512, 320, "uniform", 21)
     want = oracle_mod.gemmrc(a, b)
@@ -86,7 +86,7 @@ def test_golden_vectors(beam, oracle_mod, case):
 
 @pytest.mark.parametrize("m,n,k", [(1, 8, 8), (8, 8, 8), (127, 136, 72), (129, 264, 200), (300, 1000, 1096),
                                     (257, 520, 64), (1000, 24, 4104)])
-@pytest.mark.parametrize("tile_n,cta_pair", [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2)])
+@pytest.mark.parametrize("tile_n,cta_pair", [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2), (512, 2)])
 def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     """Edge tiles in M, N and K: out-of-range parts are zero-filled on load and masked on store, and nothing
     outside C[M,N] is written."""
@@ -142,7 +142,7 @@ def test_config2_8192_cubed(beam, oracle_mod):
     rows = np.linspace(0, m - 1, 24).astype(np.int32)
     truth = oracle_mod.gemmrc_rows_f64(a.cpu().numpy(), b.cpu().numpy(), rows)
     rms = float(np.sqrt(np.mean(truth * truth)))
-    for tb in ([128, 128], [128, 256], [256, 128], [256, 256]):
+    for tb in ([128, 128], [128, 256], [256, 128], [256, 256], [256, 512]):
         c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
         beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb)
         torch.cuda.synchronize()
