@@ -9,7 +9,7 @@ Workload (per GPU): C[8192,8192] = A[8192,8192] x B[8192,8192]^T, fp16 in, fp32 
 (weak scaling); at N = 8 this is the row-sharded 65536 x 8192 x 8192 problem.  No collective is on the timed
 path (the all-gather of C is optional and reported separately under "extras").
 
-A step is one launch of the default kernel (`cutlass_gemmrc`: 256x256 tiles on CTA pairs).  `value` is
+A step is one launch of the default kernel (`cutlass_gemmrc`: 256x512 tiles on CTA pairs).  `value` is
 whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events, max over ranks.  `e2e` is the same
 metric through the host-buffer entry (pinned host A, B -> device -> kernel -> pinned host C) with the copies
 inside the timed region.  One JSON line on stdout (rank 0).
@@ -33,8 +33,8 @@ SEED = 1234 + 2
 METRIC = "fp16 gemmrc TFLOP/s (M=8192 per GPU, N=K=8192, fp32 accumulate)"
 UNIT = "TFLOP/s"
 # DRAM bytes per launch of the default kernel at 8192^3 from the committed ncu capture
-# (profiles/gemmrc_256x256_pair_8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
-NCU_DRAM_BYTES_PER_LAUNCH = 1.128737e9 + 1.28351e8
+# (profiles/gemmrc_256x512_pair_8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
+NCU_DRAM_BYTES_PER_LAUNCH = 1.017210e9 + 1.22840e8
 
 REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
            0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting"}

@@ -188,7 +188,7 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.k_phases = 1;
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
-  p.trace = nullptr;
+  p.trace = g_trace_buffer;
   p.debug = 0;
 #endif
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles;

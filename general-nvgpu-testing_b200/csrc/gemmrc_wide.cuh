@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) BEAM_STAMP(0);
   const uint32_t cta_rank = ptx::cluster_ctarank();
   const bool leader = cta_rank == 0;
   Walk walk;
@@ -135,12 +136,20 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
         const uint32_t tile_ph = static_cast<uint32_t>(j) & 1u;
         const int lead_in = num_kb < kStages ? num_kb : kStages;  // k-blocks issued half-major
         // half 0 of the first k-blocks: needs only half 0 of the previous tile drained
-        if (!bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        {
+          BEAM_ACC_BEGIN();
+          const bool ok0 = bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
+          BEAM_ACC_END_T(13, 32);
+          if (!ok0) break;
+        }
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in && alive; ++g) {
           const uint32_t k = it + static_cast<uint32_t>(g);
           const int s = k % kStages;
-          if (!bounded_wait(full_bar(s), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull)) {
+          BEAM_ACC_BEGIN();
+          const bool landed = bounded_wait(full_bar(s), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
+          BEAM_ACC_END_T(14, 32);
+          if (!landed) {
             alive = false;
             break;
           }
@@ -149,7 +158,12 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
         }
         if (!alive) break;
         // half 1 of the same k-blocks; their stages are released here
-        if (!bounded_wait(tmem_empty_bar(1), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        {
+          BEAM_ACC_BEGIN();
+          const bool ok1 = bounded_wait(tmem_empty_bar(1), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
+          BEAM_ACC_END_T(12, 32);
+          if (!ok1) break;
+        }
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in; ++g) {
           const int s = (it + static_cast<uint32_t>(g)) % kStages;
@@ -159,7 +173,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
         it += static_cast<uint32_t>(lead_in);
         for (int kb = lead_in; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
-          if (!bounded_wait(full_bar(s), (it / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull)) {
+          BEAM_ACC_BEGIN();
+          const bool landed = bounded_wait(full_bar(s), (it / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
+          BEAM_ACC_END_T(14, 32);
+          if (!landed) {
             alive = false;
             break;
           }
@@ -178,9 +195,14 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
     uint32_t store_count = 0;
     WorkItem w;
     for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
-      if (!bounded_wait_warp(tmem_full_bar, static_cast<uint32_t>(j) & 1u, cta_abort, p.status, kFaultEpilogueWait,
-                             lane))
-        break;
+      {
+        BEAM_ACC_BEGIN();
+        const bool ready = bounded_wait_warp(tmem_full_bar, static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
+                                             kFaultEpilogueWait, lane);
+        BEAM_ACC_END(8);
+        if (!ready) break;
+      }
+      BEAM_ACC_BEGIN();
       ptx::tc_fence_after();
       const int row0 = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
 #pragma unroll 1
@@ -224,6 +246,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * static_cast<uint32_t>(h));
       }
+      BEAM_ACC_END(9);
     }
   }
 
@@ -237,6 +260,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
     ptx::tc_fence_after();
     ptx::tmem_dealloc<2>(tmem_base, S::kTmemCols);
   }
+  if (threadIdx.x == 0) BEAM_STAMP(7);
 }
 
 }  // namespace beam
