@@ -343,6 +343,29 @@ def run_ours(args):
     e2e_value = flops_step_all / (float(t.item()) / e2e_steps) * 1e-12
     e2e_ok = bool(torch.equal(hc.cuda(), c))
 
+    gather = None
+    if world > 1:
+        # Optional all-gather of C over NCCL / NVLink, outside the headline: every rank ends up with all of C.
+        from beam.sharded import all_gather_rows
+        for _ in range(2):
+            full = all_gather_rows(c, M_PER_GPU * world)
+        torch.cuda.synchronize()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            full = all_gather_rows(c, M_PER_GPU * world)
+        g1.record()
+        torch.cuda.synchronize()
+        tg = torch.tensor([g0.elapsed_time(g1) / 5], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        gather_ms = float(tg.item())
+        recv_bytes = 2.0 * M_PER_GPU * N * (world - 1)
+        gather = {"ms": gather_ms, "bytes_received_per_gpu": recv_bytes,
+                  "GBps_in_per_gpu": recv_bytes / (gather_ms * 1e-3) * 1e-9,
+                  "tflops_gemm_then_gather": flops_step_all / ((ms_step + gather_ms) * 1e-3) * 1e-12}
+        del full
+
     if rank == 0:
         burst = ms_total < 500.0  # a short run sits in the burst regime, a long one under the power cap
         peak = peaks["burst"] if burst or not peaks["sustained"] else peaks["sustained"]
@@ -368,6 +391,8 @@ def run_ours(args):
                          "algorithmic_flops_per_launch": 2.0 * M_PER_GPU * N * K,
                          "frac_of_spec_2250": per_gpu / 2250.0},
         }
+        if gather is not None:
+            line["extras"] = {"all_gather_c": gather}
         if world == 1:
             from oracle import build_oracle
             build_oracle.build()
