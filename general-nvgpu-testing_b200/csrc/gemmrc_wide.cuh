@@ -29,7 +29,10 @@ struct WideShape {
   static constexpr int kTmemCols = 512;
   static constexpr int kBarBytes = 512;
   static constexpr int kStoreBufBytes = 32 * 128;
-  static constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
+  // A 3-deep ring leaves room for four staging buffers per epilogue warp (stores rarely wait for a buffer);
+  // a 4-deep ring for two.
+  static constexpr int kBufsPerWarp = (kStages <= 3) ? 4 : 2;
+  static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;
   static constexpr int kThreads = 192;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
@@ -221,9 +224,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
             out[16 + q] = ptx::pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
           }
           if (col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m) {
-            const uint32_t buf = staging_base + (quad * 2u + (store_count & 1u)) * S::kStoreBufBytes;
-            if (store_count >= 2) {
-              if (lane == 0) ptx::tma_store_wait_read<1>();
+            constexpr uint32_t kBufs = S::kBufsPerWarp;
+            const uint32_t buf = staging_base + (quad * kBufs + (store_count % kBufs)) * S::kStoreBufBytes;
+            if (store_count >= kBufs) {
+              if (lane == 0) ptx::tma_store_wait_read<kBufs - 1>();
               __syncwarp();
             }
             const uint32_t row_addr = buf + lane * 128u;
