@@ -28,6 +28,7 @@ __all__ = [
     "cutlass_parallel_gemmrc_lnr",
     "gemmrc",
     "gemmrc_host",
+    "gemmrc_allgather",
     "BeamError",
     "library_path",
 ]
@@ -92,6 +93,7 @@ def _load():
     L.beam_gemmrc_layernorm_workspace_bytes.argtypes = [i, i, i]
     L.beam_gemmrc_layernorm.argtypes = [vp, vp, vp, vp, vp, f, i, i, i, vp, sz, vp]
     L.beam_gemmrc_fp16_host.argtypes = [vp, vp, vp, i, i, i]
+    L.beam_gemmrc_fp16_allgather.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp]
     _lib = L
     return L
 
@@ -260,6 +262,30 @@ def cutlass_parallel_gemmrc_lnr(a, b, c, gamma, beta, eps=1e-5):
                                      float(eps), m, n, k, ws.data_ptr(), ws.numel(), _stream(a))
     if st != BEAM_OK:
         _raise(st, "beam_gemmrc_layernorm")
+
+
+def gemmrc_allgather(a_local, b, gathered_ptrs, rank, n, tile_n=0, cta_pair=0, stages=0, group_m=0):
+    """Fused row-sharded GEMM + all-gather: this rank's a_local[M_local,K] @ b[N,K].T is written into row block `rank`
+    of every rank's gathered C[world * M_local, N]; gathered_ptrs[d] is rank d's buffer as a device pointer valid in
+    this process (see beam.sharded.GatheredC).  Asynchronous; complete once all ranks' kernels have finished."""
+    for name, t in (("a_local", a_local), ("b", b)):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous() and t.dtype == torch.float16
+                and t.dim() == 2):
+            raise TypeError("%s must be a contiguous 2-D CUDA float16 tensor" % name)
+    m, k = a_local.shape
+    if b.shape != (n, k):
+        raise ValueError("b must be [N,K]=(%d,%d), got %s" % (n, k, tuple(b.shape)))
+    world = len(gathered_ptrs)
+    arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in gathered_ptrs])
+    cfg = None
+    if tile_n or cta_pair or stages or group_m:
+        cfg = ctypes.byref(beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m)))
+    L = _load()
+    with torch.cuda.device(a_local.device):
+        st = L.beam_gemmrc_fp16_allgather(a_local.data_ptr(), b.data_ptr(), arr, world, int(rank), int(m), int(n), int(k),
+                                          cfg, _stream(a_local))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_fp16_allgather")
 
 
 def gemmrc_host(a, b, c):

@@ -51,3 +51,36 @@ def all_gather_rows(c_local: torch.Tensor, m: int, group=None) -> torch.Tensor:
                 full[s:e].copy_(c_local)
             dist.broadcast(full[s:e], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
     return full
+
+
+class GatheredC:
+    """The gathered C[world * m_local, n] of a row-sharded GEMM, allocated as torch symmetric memory so that every
+    rank holds device pointers to every other rank's copy.  `tensor` is this rank's copy; `ptrs[d]` is rank d's."""
+
+    def __init__(self, m_local: int, n: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.m_local, self.n = int(m_local), int(n)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.tensor = symm_mem.empty((self.world * self.m_local, self.n), dtype=torch.float16, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def barrier(self):
+        """Stream-ordered barrier across the ranks: after it, every rank's stores issued before it have landed."""
+        self.handle.barrier()
+
+
+def gemmrc_allgather(a_local: torch.Tensor, b: torch.Tensor, gathered: "GatheredC", **knobs) -> torch.Tensor:
+    """gathered.tensor (on every rank) = concat over ranks of a_local_r @ b.T, computed and gathered by ONE kernel per
+    rank: each finished tile is TMA-stored into all ranks' buffers over NVLink while the main loop continues.
+    Returns gathered.tensor; it is complete after gathered.barrier() (called here)."""
+    from . import _C
+    if a_local.shape[0] != gathered.m_local or b.shape[0] != gathered.n:
+        raise ValueError("a_local must have %d rows and b %d rows" % (gathered.m_local, gathered.n))
+    gathered.barrier()  # nobody may still be reading the previous contents
+    _C.gemmrc_allgather(a_local, b, gathered.ptrs, gathered.rank, gathered.n, **knobs)
+    gathered.barrier()
+    return gathered.tensor

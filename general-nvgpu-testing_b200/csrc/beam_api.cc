@@ -62,6 +62,24 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
   return launch_gemmrc(A, B, C, m, n, k, plan, static_cast<cudaStream_t>(stream));
 }
 
+int beam_gemmrc_fp16_allgather(const void* A_local, const void* B, void* const* C_gathered, int world, int rank,
+                               int m_local, int n, int k, const beam_gemm_cfg* cfg, void* stream) {
+  GemmPlan plan;
+  if (cfg) {
+    if (cfg->tile_n) plan.tile_n = cfg->tile_n;
+    if (cfg->cta_pair) plan.cta_pair = cfg->cta_pair;
+    plan.stages = cfg->stages;
+    plan.group_m = cfg->group_m;
+    if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
+    if (plan.stages < 0 || plan.group_m < 0) return BEAM_ERR_INVALID_ARG;
+  } else {
+    const long long wide_tiles = static_cast<long long>((m_local + 255) / 256) * ((n + 511) / 512);
+    if (m_local > 0 && n > 0 && wide_tiles >= 4 * 74) plan.tile_n = 512;
+  }
+  return launch_gemmrc_allgather(A_local, B, C_gathered, world, rank, m_local, n, k, plan,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 int beam_custom_gemmrc_128x128(const void* A, const void* B, void* C, int m, int n, int k, void* stream) {
   GemmPlan plan;
   plan.tile_n = 128;

@@ -31,6 +31,8 @@ struct ExtraArgs {
   int flags = 0;
   int raster = 0;
   int k_phases = 0;
+  const void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // fused all-gather
+  int n_peers = 0;
   float2* row_part = nullptr;
   int* tickets = nullptr;
   int* ln_queue = nullptr;
@@ -86,6 +88,14 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
                             static_cast<uint64_t>(n), 32, 32);
   }
   if (st != BEAM_OK) return st;
+  if (kMode == kModeGemm) {
+    for (int d = 0; d < ex.n_peers; ++d) {
+      st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                          static_cast<uint64_t>(n), 32, 64, true);
+      if (st != BEAM_OK) return st;
+    }
+    p.n_peers = ex.n_peers;
+  }
   p.c = static_cast<__half*>(C);
   p.scratch = ex.scratch;
   p.row_part = ex.row_part;
@@ -173,6 +183,12 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n), 32,
                       64, true);
   if (st != BEAM_OK) return st;
+  for (int d = 0; d < ex.n_peers; ++d) {
+    st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                        static_cast<uint64_t>(n), 32, 64, true);
+    if (st != BEAM_OK) return st;
+  }
+  p.n_peers = ex.n_peers;
   p.c = static_cast<__half*>(C);
   p.m = m;
   p.n = n;
@@ -232,14 +248,13 @@ int validate_gemm_args(const void* A, const void* B, const void* C, int m, int n
     return launch_instance<BN_, ST_, CTA_, kModeGemm>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, \
                                                       stream);
 
-int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
-                  cudaStream_t stream) {
+static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
+                            ExtraArgs ex, cudaStream_t stream) {
   int st = validate_gemm_args(A, B, C, m, n, k);
   if (st != BEAM_OK) return st;
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
-  ExtraArgs ex;
   ex.l2_hints = plan.l2_hints;
   ex.raster = plan.raster;
   ex.k_phases = plan.k_phases;
@@ -266,6 +281,34 @@ int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, co
   return BEAM_ERR_UNSUPPORTED;
 }
 #undef BEAM_GEMM_CASE
+
+int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
+                  cudaStream_t stream) {
+  return launch_gemmrc_ex(A, B, C, m, n, k, plan, ExtraArgs(), stream);
+}
+
+// Every destination (this GPU included) receives the rank's block at rows [rank * m, (rank + 1) * m) of its
+// gathered buffer.  The tensor maps start at that block and span m rows, so the copy engine clips a tile that
+// overhangs the block instead of spilling into the next rank's rows.
+int launch_gemmrc_allgather(const void* A, const void* B, void* const* gathered, int world, int rank, int m, int n,
+                            int k, const GemmPlan& plan, cudaStream_t stream) {
+  if (!gathered || world < 1 || world > 8 || rank < 0 || rank >= world) return BEAM_ERR_INVALID_ARG;
+  if (m <= 0 || n <= 0 || k <= 0) return BEAM_ERR_INVALID_ARG;
+  const size_t block_bytes = static_cast<size_t>(m) * static_cast<size_t>(n) * 2;
+  ExtraArgs ex;
+  void* local = nullptr;
+  for (int i = 0; i < world; ++i) {
+    const int d = (rank + i) % world;  // self first, then the peers starting with the next rank
+    if (!gathered[d]) return BEAM_ERR_INVALID_ARG;
+    char* block = static_cast<char*>(gathered[d]) + static_cast<size_t>(rank) * block_bytes;
+    if (!aligned16(block)) return BEAM_ERR_ALIGNMENT;
+    if (i == 0)
+      local = block;
+    else
+      ex.peer_c[ex.n_peers++] = block;
+  }
+  return launch_gemmrc_ex(A, B, local, m, n, k, plan, ex, stream);
+}
 
 // ---------------------------------------------------------------------------------- split-K
 int splitk_tile_n(int n, int tile_n) {

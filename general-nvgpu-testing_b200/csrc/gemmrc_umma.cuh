@@ -43,6 +43,8 @@ struct GemmParams {
   CUtensorMap tm_b;  // B  [N, K], box (BN / kCta) x 64, 128 B swizzle
   CUtensorMap tm_c;  // C  [M, N] fp16, store box 32 rows x 64 columns, 128 B swizzle
   CUtensorMap tm_s;  // scratch [slices][M][N] fp32, store box 1 x 32 rows x 32 columns, 128 B swizzle
+  CUtensorMap tm_peer[7];  // fused all-gather: this rank's row block inside each peer GPU's gathered C
+  int n_peers;             // 0 = plain GEMM; else every C box is also stored to that many peers
   __half* c;         // fp16 output [M, ldc]
   float* scratch;    // split-K: partials [slices][M][N]; LayerNorm: fp32 panel store [M][N]
   float2* row_part;  // LayerNorm: (mean, M2) of every row over each N tile, [M][n_tiles]
@@ -167,6 +169,14 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk,
     w.kb1 = static_cast<int>(static_cast<long long>(num_kb) * (w.slice + 1) / p.slices);
     return true;
   }
+}
+
+// Stores one staged 32 x 64 fp16 box of C: to this GPU's C and, in the fused all-gather, to the same place in
+// every peer's gathered buffer (plain per-destination TMA stores over NVLink; one bulk group for all of them).
+__device__ __forceinline__ void store_c_box(const GemmParams& p, uint32_t buf, int x, int y) {
+  ptx::tma_store_2d_hint(&p.tm_c, buf, x, y, ptx::l2_policy(p.hint_c));
+  for (int d = 0; d < p.n_peers; ++d) ptx::tma_store_2d(&p.tm_peer[d], buf, x, y);
+  ptx::tma_store_commit();
 }
 
 // Chan's parallel update of (count, mean, M2) with a block of `nb` values whose own mean and M2 are given.
@@ -676,12 +686,12 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if constexpr (kMode == kModeGemm)
-              ptx::tma_store_2d_hint(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32,
-                                     ptx::l2_policy(p.hint_c));
-            else
+            if constexpr (kMode == kModeGemm) {
+              store_c_box(p, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
+            } else {
               ptx::tma_store_3d(&p.tm_s, buf, col0 + c, row0 + static_cast<int>(quad) * 32, w.slice);
-            ptx::tma_store_commit();
+              ptx::tma_store_commit();
+            }
           }
           ++store_count;
         }

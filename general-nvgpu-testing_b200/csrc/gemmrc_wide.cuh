@@ -237,11 +237,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
                                 out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-              ptx::tma_store_2d_hint(&p.tm_c, buf, col0 + c, row0 + static_cast<int>(quad) * 32,
-                                     ptx::l2_policy(p.hint_c));
-              ptx::tma_store_commit();
-            }
+            if (lane == 0) store_c_box(p, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
             ++store_count;
           }
         }

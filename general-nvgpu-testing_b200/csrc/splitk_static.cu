@@ -108,6 +108,7 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.hint_a = 0;
   p.hint_b = 0;
   p.hint_c = 0;
+  p.n_peers = 0;
   p.flags = 0;
   p.raster = 0;
   p.k_phases = 1;

@@ -88,6 +88,17 @@ BEAM_API int beam_device_status(int clear, int* fault_word_out);
 BEAM_API int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k, const beam_gemm_cfg* cfg,
                      void* stream);
 
+/* Row-sharded GEMM fused with the all-gather of C (no counterpart in the reference, which is single-GPU).
+ * Rank `rank` of `world` (<= 8, one process per GPU) multiplies its m_local rows of A by all of B and stores
+ * every finished tile of C straight into row block `rank` of each GPU's gathered C[world * m_local, N]:
+ * C_gathered[d] is the device pointer, valid in THIS process, of rank d's gathered buffer (its own for
+ * d == rank, peer-mapped memory for the others: CUDA IPC / VMM / torch symmetric memory).  The epilogue issues
+ * one plain TMA store per destination over NVLink, so the gather overlaps the main loop tile by tile.
+ * The call returns after the launch; the gathered buffers are complete once every rank's kernel has
+ * finished (a host- or stream-level barrier across the ranks after it).  m_local must be the same on all ranks. */
+BEAM_API int beam_gemmrc_fp16_allgather(const void* A_local, const void* B, void* const* C_gathered, int world,
+                                        int rank, int m_local, int n, int k, const beam_gemm_cfg* cfg, void* stream);
+
 /* Registry name `custom_gemmrc_128x128` — replaces entry_custom_gemmrc_128x128
  * (cuda/cute_kernels/cute_gemm_128x128.cu:193-205, declared cuda/cute_kernels/main.cc:13-14):
  * 128x128 output tile per CTA. */

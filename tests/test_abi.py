@@ -73,6 +73,21 @@ def test_argument_validation_needs_no_gpu(lib):
     assert g(p, p, p, 64, 64, 64, 128, 96, 64, 64, None) == 2
 
 
+def test_allgather_entry_validates_without_gpu(lib):
+    vp, i = ctypes.c_void_p, ctypes.c_int
+    f = lib.beam_gemmrc_fp16_allgather
+    f.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, i, i, i, vp, vp]
+    keep, p = _aligned_buffer(1 << 16)
+    ptrs = (vp * 2)(vp(p), vp(p))
+    assert f(p, p, None, 2, 0, 64, 64, 64, None, None) == 1          # no destination list
+    assert f(p, p, ptrs, 9, 0, 64, 64, 64, None, None) == 1          # more than 8 ranks
+    assert f(p, p, ptrs, 2, 2, 64, 64, 64, None, None) == 1          # rank out of range
+    assert f(p, p, ptrs, 2, 0, 0, 64, 64, None, None) == 1           # empty block
+    holes = (vp * 2)(vp(p), vp(None))
+    assert f(p, p, holes, 2, 0, 64, 64, 64, None, None) == 1         # a missing peer pointer
+    assert f(p, p, ptrs, 2, 1, 64, 60, 64, None, None) == 3          # N not a multiple of 8
+
+
 def test_splitk_sizing_functions(lib):
     i = ctypes.c_int
     ws = lib.beam_gemmrc_splitk_workspace_bytes

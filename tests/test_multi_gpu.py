@@ -1,0 +1,60 @@
+"""Two-GPU test of the fused GEMM + all-gather (pytest -m gpu on a box with at least two GPUs; skipped otherwise).
+Each rank multiplies its row block and the kernel's epilogue stores every tile into both ranks' gathered buffers
+through peer-mapped (symmetric) memory; the result must equal the plain sharded GEMM followed by an NCCL all-gather."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(here, "general-nvgpu-testing_b200"))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import beam
+        from beam.sharded import GatheredC, all_gather_rows, gemmrc_allgather
+        for (m_local, n, k, knobs) in ((512, 1024, 512, {}), (300, 776, 264, {"tile_n": 256, "cta_pair": 2}),
+                                       (2048, 4096, 1024, {"tile_n": 512, "cta_pair": 2})):
+            g = torch.Generator(device="cuda").manual_seed(100 + rank)
+            a = (torch.randn(m_local, k, device="cuda", generator=g) * 0.1).half()
+            gb = torch.Generator(device="cuda").manual_seed(7)
+            b = (torch.randn(n, k, device="cuda", generator=gb) * 0.1).half()
+            c_local = torch.empty(m_local, n, dtype=torch.float16, device="cuda")
+            beam.gemmrc(a, b, c_local, **knobs)
+            want = all_gather_rows(c_local, m_local * world)
+            gathered = GatheredC(m_local, n)
+            gathered.tensor.fill_(3.0)
+            got = gemmrc_allgather(a, b, gathered, **knobs)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), "rank %d shape %s" % (rank, (m_local, n, k))
+        st, word = beam.device_status()
+        assert (st, word) == (0, 0)
+        open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_gemm_allgather_two_gpus(tmp_path, built_library):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
