@@ -55,8 +55,7 @@ class beam_gemm_cfg(ctypes.Structure):
         ("max_ctas", ctypes.c_int),
         ("l2_hints", ctypes.c_int),
         ("flags", ctypes.c_int),
-        ("raster", ctypes.c_int),
-        ("k_phases", ctypes.c_int),
+        ("reserved", ctypes.c_int * 2),
     ]
 
 
@@ -193,11 +192,10 @@ def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 6
     _run("beam_cutlass_gemmrc_spec", a, b, c, tbm, tbn, wm, wn)
 
 
-def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, raster=0, k_phases=0):
+def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0):
     """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over."""
     m, n, k = _check_abc(a, b, c)
-    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), 0,
-                        int(raster), int(k_phases))
+    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), 0)
     L = _load()
     with torch.cuda.device(a.device):
         st = L.beam_gemmrc_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg), _stream(a))

@@ -52,11 +52,8 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.group_m = cfg->group_m;
     plan.max_ctas = cfg->max_ctas;
     plan.l2_hints = cfg->l2_hints;
-    plan.raster = cfg->raster;
-    plan.k_phases = cfg->k_phases;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
-    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0 || plan.l2_hints < 0 || plan.l2_hints > 222 || plan.raster < 0 ||
-        plan.raster > 1 || plan.k_phases < 0 || plan.k_phases > 8)
+    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0 || plan.l2_hints < 0 || plan.l2_hints > 222)
       return BEAM_ERR_INVALID_ARG;
   }
   return launch_gemmrc(A, B, C, m, n, k, plan, static_cast<cudaStream_t>(stream));

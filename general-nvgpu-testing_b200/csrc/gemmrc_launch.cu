@@ -29,8 +29,6 @@ struct ExtraArgs {
   int slices = 1;
   int l2_hints = 0;
   int flags = 0;
-  int raster = 0;
-  int k_phases = 0;
   const void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // fused all-gather
   int n_peers = 0;
   float2* row_part = nullptr;
@@ -117,12 +115,6 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.hint_b = ex.l2_hints % 10;
   p.hint_c = (ex.l2_hints / 100) % 10;
   p.flags = ex.flags;
-  {
-    int ph = ex.k_phases > 0 ? ex.k_phases : 1;
-    const int num_kb = (k + S::kBK - 1) / S::kBK;
-    while (ph > 1 && (ph > num_kb || (ph & (ph - 1)) != 0)) ph >>= 1;  // a power of two, at most one offset per k-block
-    p.k_phases = ph < 1 ? 1 : ph;
-  }
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
   p.trace = g_trace_buffer;
@@ -153,8 +145,6 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;
   }
-  // The split raster indexes workers by SM id: only valid when the grid fills the device, one CTA per SM.
-  p.raster = (ex.raster == 1 && clusters * kCta == ctx->sm_count && p.m_tiles >= 2) ? 1 : 0;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
@@ -201,7 +191,6 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
   p.hint_c = (ex.l2_hints / 100) % 10;
-  p.k_phases = 1;
   p.status = ctx->status_word;
 #ifdef BEAM_TRACE
   p.trace = g_trace_buffer;
@@ -256,8 +245,6 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   if (!ctx) return st;
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
-  ex.raster = plan.raster;
-  ex.k_phases = plan.k_phases;
   if (plan.tile_n == 512) {
     if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
     if (plan.stages == 0 || plan.stages == 4)

@@ -11,8 +11,6 @@ struct GemmPlan {
   int stages = 0;     // 0 = deepest ring that fits
   int group_m = 0;    // 0 = default rasterisation group
   int max_ctas = 0;   // 0 = whole device
-  int k_phases = 0;   // K-loop starting offsets per tile: 0 = default (1), else 1, 2, 4 or 8
-  int raster = 0;     // 0 grouped walk, 1 split M between the two halves of the SM id space
   int l2_hints = 0;   // decimal digits: tens = A loads, ones = B loads; 0 normal, 1 evict-first, 2 evict-last
 };
 

@@ -63,8 +63,6 @@ struct GemmParams {
   int hint_b;   // same for the B loads
   int hint_c;   // same for the C stores (GEMM mode)
   int flags;    // BEAM_FLAG_* bits of the call
-  int raster;   // GEMM: 0 = one grouped walk over all tiles; 1 = the two halves of the SM id space split M
-  int k_phases; // GEMM, LayerNorm: number of distinct K-loop starting offsets (power of two, >= 1)
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
@@ -135,10 +133,9 @@ struct WorkItem {
 //              in flight together share A rows and B rows in L2 (the reference's CTA remap at
 //              cute_gemm_128x128.cu:23-33, restated for a persistent grid).
 //   split-K:   items are (tile, slice), slice fastest; k-blocks are dealt out as evenly as possible.
-// How one CTA (pair) walks the work: item j is `first + j * stride` within the M-tile range
-// [m_base, m_base + m_count) (the whole problem unless the raster splits it between the two halves of the chip).
+// How one CTA (pair) walks the work: item j is `first + j * stride`.
 struct Walk {
-  int first, stride, m_base, m_count;
+  int first, stride;
 };
 
 template <int kMode>
@@ -149,13 +146,13 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk,
   w.kb1 = num_kb;
   if constexpr (kMode != kModeSplitK) {
     const int t = first + j * stride;
-    if (t >= walk.m_count * p.n_tiles) return false;
+    if (t >= p.m_tiles * p.n_tiles) return false;
     const int per_group = p.group_m * p.n_tiles;
     const int g = t / per_group;
     const int first_m = g * p.group_m;
-    const int rows = min(p.group_m, walk.m_count - first_m);
+    const int rows = min(p.group_m, p.m_tiles - first_m);
     const int r = t - g * per_group;
-    w.mt = walk.m_base + first_m + r % rows;
+    w.mt = first_m + r % rows;
     w.nt = r / rows;
     return true;
   } else {
@@ -359,28 +356,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   Walk walk;
   walk.stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   walk.first = (kCta == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  walk.m_base = 0;
-  walk.m_count = p.m_tiles;
-  if constexpr (kMode == kModeGemm) {
-    if (p.raster == 1) {
-      // Split raster: the SMs with the lower half of the SM ids take the upper half of the M tiles' rows...
-      // each half of the chip then touches only its own rows of A, so those lines are cached once, not in
-      // both halves of the L2.  One CTA per SM and a grid that fills the device (checked by the launcher)
-      // make SM id / kCta a dense worker index; a pair sits on SMs (2t, 2t + 1).
-      uint32_t smid, nsmid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      asm volatile("mov.u32 %0, %%nsmid;" : "=r"(nsmid));
-      const int workers = static_cast<int>(nsmid) / kCta;
-      const int v = static_cast<int>(smid) / kCta;
-      const int half = workers / 2;
-      const int upper = v >= half ? 1 : 0;
-      walk.first = v - upper * half;
-      walk.stride = upper ? workers - half : half;
-      const int m_half = p.m_tiles / 2;
-      walk.m_base = upper ? m_half : 0;
-      walk.m_count = upper ? p.m_tiles - m_half : m_half;
-    }
-  }
 
   // ---- shared-memory carve-up (tile buffers need 1024-byte alignment for the 128 B swizzle)
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -432,11 +407,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       if (work_item<kMode>(p, walk, 0, num_kb, w0)) {
         const int row_a = w0.mt * S::kBM;
         const int row_b = w0.nt * BN;
-        const int nkb0 = w0.kb1 - w0.kb0;
-        const int rot0 = (kMode == kModeSplitK) ? 0 : ((w0.mt + w0.nt) & (p.k_phases - 1)) * (nkb0 / p.k_phases);
-        for (; static_cast<int>(preloaded) < nkb0 && preloaded < static_cast<uint32_t>(kStages); ++preloaded) {
-          const int i0 = static_cast<int>(preloaded);
-          const int kb = w0.kb0 + (i0 + rot0 < nkb0 ? i0 + rot0 : i0 + rot0 - nkb0);
+        for (int kb = w0.kb0; kb < w0.kb1 && preloaded < static_cast<uint32_t>(kStages); ++kb, ++preloaded) {
           const int s = static_cast<int>(preloaded);
           ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
           ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, ptx::l2_policy(p.hint_a));
@@ -474,18 +445,12 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           row_b = static_cast<int>(cta_rank) * S::kBRows;
         }
 #endif
-        // Rotated K loop: tile (mt, nt) starts at k-block rot and wraps.  Tiles that share rows of A (same mt)
-        // or of B (same nt) start at different offsets, so a shared line is touched every 1/k_phases of a
-        // wave instead of once per wave, close enough together to still be in L2 the next time.
-        const int nkb = w.kb1 - w.kb0;
-        const int rot = (kMode == kModeSplitK) ? 0 : ((w.mt + w.nt) & (p.k_phases - 1)) * (nkb / p.k_phases);
-        int i = 0;
+        int kb = w.kb0;
         if (j == 0) {  // these are already in flight
-          i = static_cast<int>(preloaded);
+          kb += static_cast<int>(preloaded);
           it = preloaded;
         }
-        for (; i < nkb; ++i, ++it) {
-          const int kb = w.kb0 + (i + rot < nkb ? i + rot : i + rot - nkb);
+        for (; kb < w.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {

@@ -51,8 +51,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
   Walk walk;
   walk.stride = static_cast<int>(gridDim.x >> 1);
   walk.first = static_cast<int>(blockIdx.x >> 1);
-  walk.m_base = 0;
-  walk.m_count = p.m_tiles;
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));

@@ -110,8 +110,6 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.hint_c = 0;
   p.n_peers = 0;
   p.flags = 0;
-  p.raster = 0;
-  p.k_phases = 1;
   p.status = fault_word;
 #ifdef BEAM_TRACE
   p.trace = nullptr;

@@ -57,11 +57,7 @@ typedef struct beam_gemm_cfg {
   int l2_hints;       /* L2 eviction policy, three decimal digits: hundreds = C stores, tens = A loads,
                          ones = B loads; 0 normal, 1 evict-first, 2 evict-last                      */
   int flags;          /* BEAM_FLAG_* bits                                                       */
-  int raster;         /* large GEMM: 0 one grouped walk over all tiles; 1 the two halves of the SM id
-                         space each take half of the M tiles                                     */
-  int k_phases;       /* large GEMM: tiles start their K loop at one of this many evenly spaced
-                         offsets (1, 2, 4 or 8), chosen by (m_tile + n_tile).  A tuning knob: on B200
-                         anything but 1 (the default, also for 0) raises DRAM traffic.             */
+  int reserved[2];
 } beam_gemm_cfg;
 
 /* Split-K only.  The caller guarantees that A and B are not outputs of the kernel that immediately precedes
