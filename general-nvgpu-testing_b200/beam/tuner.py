@@ -134,6 +134,47 @@ class OperatorTuner:
         self.gemm_ops.extend(self._get_gemm_specs())
         self.gemm_ops.extend(self._get_gemm_splitk_specs())
 
+    # ---- persistence (the reference keeps its cache in memory only: python/beam/tuner.py:50,97,136)
+    def _device_key(self) -> str:
+        try:
+            return torch.cuda.get_device_name(torch.cuda.current_device())
+        except Exception:
+            return "no-device"
+
+    def save(self, path: str) -> None:
+        """Writes the tuned choices as JSON: {device name: {"gemm(M,N,K,)": [operator description, TFLOP/s]}}.  Entries
+        of other devices already in the file are kept."""
+        import json
+        import os
+        data = {}
+        if os.path.exists(path):
+            with open(path) as f:
+                data = json.load(f)
+        mine = data.setdefault(self._device_key(), {})
+        for key, (op, tflops) in self.cache.items():
+            mine[key] = [str(op), float(tflops)]
+        tmp = path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(data, f, indent=1, sort_keys=True)
+        os.replace(tmp, path)
+
+    def load(self, path: str) -> int:
+        """Reads choices saved for this device; an entry is used only if its operator is still in the search space.
+        Returns how many entries were taken."""
+        import json
+        import os
+        if not os.path.exists(path):
+            return 0
+        with open(path) as f:
+            data = json.load(f)
+        by_name = {str(op): op for op in self.gemm_ops}
+        taken = 0
+        for key, (name, tflops) in data.get(self._device_key(), {}).items():
+            if name in by_name:
+                self.cache[key] = (by_name[name], float(tflops))
+                taken += 1
+        return taken
+
     def get_hash(self, name: str, args: List) -> str:
         ret = name + "("
         for arg in args:

@@ -99,6 +99,23 @@ def test_operator_and_tuner_interface():
     assert tuner.tune([4, 4, 4]) == ("op", 1.0)                          # cache hit needs no GPU
 
 
+def test_tuner_cache_persistence(tmp_path):
+    import beam
+    path = str(tmp_path / "tuned.json")
+    t1 = beam.OperatorTuner()
+    op = t1.gemm_ops[3]
+    t1.cache["gemm(8192,8192,8192,)"] = (op, 1234.5)
+    t1.cache["gemm(64,64,131072,)"] = (t1.gemm_ops[-1], 7.25)
+    t1.save(path)
+    t1.save(path)  # idempotent, keeps the file valid
+    t2 = beam.OperatorTuner()
+    assert t2.load(path) == 2
+    got_op, got_tf = t2.tune([8192, 8192, 8192])          # served from the loaded cache, no GPU needed
+    assert str(got_op) == str(op) and got_tf == 1234.5
+    assert str(t2.cache["gemm(64,64,131072,)"][0]) == str(t1.gemm_ops[-1])
+    assert beam.OperatorTuner().load(str(tmp_path / "missing.json")) == 0
+
+
 def test_row_block_partition():
     from beam.sharded import row_block
     for m, world in ((65536, 8), (65536, 4), (10, 4), (3, 8), (0, 2), (8192, 1)):
