@@ -29,6 +29,7 @@ struct ExtraArgs {
   int slices = 1;
   int l2_hints = 0;
   int flags = 0;
+  int fold = 0;
   const void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // fused all-gather
   int n_peers = 0;
   float2* row_part = nullptr;
@@ -72,17 +73,20 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   }
 
   GemmParams p = {};
+  const bool fold = kMode == kModeSplitK && BN == 128 && kCta == 1 && ex.fold != 0;
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
-                          static_cast<uint64_t>(k), S::kBM, S::kBK, true);
+                          static_cast<uint64_t>(k), fold ? S::kBM / 2 : S::kBM, S::kBK, true);
   if (st != BEAM_OK) return st;
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
-                      S::kBRows, S::kBK, true);
+                      fold ? S::kBRows / 2 : S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
+  p.fold = fold ? 1 : 0;
   if (kMode == kModeGemm) {
     st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n),
                         32, 64, true);
   } else {
-    st = encode_tmap_3d_f32(&p.tm_s, ex.scratch, static_cast<uint64_t>(ex.slices), static_cast<uint64_t>(m),
+    st = encode_tmap_3d_f32(&p.tm_s, ex.scratch, static_cast<uint64_t>(ex.slices) * (fold ? 2 : 1),
+                            static_cast<uint64_t>(m),
                             static_cast<uint64_t>(n), 32, 32);
   }
   if (st != BEAM_OK) return st;
@@ -307,8 +311,9 @@ int splitk_tile_n(int n, int tile_n) {
 // slice, so that the fill of the TMA ring is amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:44-57,
 // targets the 108 SMs of an A100 and rounds to half waves.)
 // Calls that carry BEAM_FLAG_INPUTS_STABLE overlap with their neighbours on the stream, so the grid is sized by
-// bytes instead: about 650 KB of operand traffic per CTA, which leaves room for two or three consecutive calls
-// to stream side by side (measured optimum on B200 for 128x256x65536 and 64x64x131072).
+// bytes instead: about 650 KB of operand traffic per CTA (820 KB when the problem runs folded), which leaves room
+// for two or three consecutive calls to stream side by side (measured optimum on B200 for 128x256x65536 and
+// 64x64x131072).
 int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
   const int bn = splitk_tile_n(n, tile_n);
   const long long m_tiles = (m + 127) / 128, n_tiles = (n + bn - 1) / bn;
@@ -326,7 +331,8 @@ int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
   if (flags & BEAM_FLAG_INPUTS_STABLE) {
     // every N tile re-reads its rows of A, every M tile its rows of B (from L2 after the first reader)
     const double bytes = 2.0 * k * (static_cast<double>(m) * n_tiles + static_cast<double>(n) * m_tiles);
-    const long long by_bytes = static_cast<long long>(bytes / (650.0 * 1024.0) / static_cast<double>(tiles) + 0.5);
+    const double per_cta = splitk_folds(m, n, tile_n) ? 820.0 * 1024.0 : 650.0 * 1024.0;  // folded rings hold more of K
+    const long long by_bytes = static_cast<long long>(bytes / per_cta / static_cast<double>(tiles) + 0.5);
     if (by_bytes < s) s = by_bytes;
   }
   const long long cap = num_kb / 4 > 0 ? num_kb / 4 : 1;
@@ -336,17 +342,24 @@ int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
   return static_cast<int>(s);
 }
 
+// Problems with M, N <= 64 run "folded" (two k-blocks per UMMA, see gemmrc_umma.cuh) unless the caller insists
+// on a 128- or 256-wide tile: K is then dealt out in steps of 128, and every slice leaves two partial planes.
+bool splitk_folds(int m, int n, int tile_n) { return m <= 64 && n <= 64 && (tile_n == 0 || tile_n == 64); }
+
 int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested, int flags) {
   const int num_kb = (k + 63) / 64;
-  if (requested > 0 && requested <= num_kb && requested <= 1024) return requested;
-  return splitk_heuristic(m, n, k, tile_n, flags);
+  const int steps = splitk_folds(m, n, tile_n) ? (num_kb + 1) / 2 : num_kb;
+  if (requested > 0 && requested <= num_kb && requested <= 1024) return requested <= steps ? requested : steps;
+  const int h = splitk_heuristic(m, n, k, tile_n, flags);
+  return h <= steps ? h : steps;
 }
 
 size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // sized for the plain heuristic, which never picks fewer slices than the overlapped one
   const int s = splitk_resolve_slices(m, n, k, tile_n, slices, 0);
-  return static_cast<size_t>(s) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+  const size_t planes = static_cast<size_t>(s) * (splitk_folds(m, n, tile_n) ? 2 : 1);
+  return planes * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
 }
 
 int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, int tile_n, int slices,
@@ -357,9 +370,11 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   if (m > 65535) return BEAM_ERR_UNSUPPORTED;  // the reduction grid has one block row per output row
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
-  const int bn = splitk_tile_n(n, tile_n);
-  const int s = splitk_resolve_slices(m, n, k, bn, slices, flags);
-  const size_t need = static_cast<size_t>(s) * m * n * sizeof(float);
+  const bool fold = splitk_folds(m, n, tile_n);
+  const int bn = fold ? 128 : splitk_tile_n(n, tile_n);
+  const int s = splitk_resolve_slices(m, n, k, tile_n, slices, flags);
+  const int planes = fold ? 2 * s : s;
+  const size_t need = static_cast<size_t>(planes) * m * n * sizeof(float);
   if (!workspace || workspace_bytes < need) return BEAM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
 
@@ -367,6 +382,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   ex.scratch = static_cast<float*>(workspace);
   ex.slices = s;
   ex.flags = flags;
+  ex.fold = fold ? 1 : 0;
   if (bn == 64)
     st = launch_instance<64, 8, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
   else if (bn == 128)
@@ -388,7 +404,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float*>(workspace),
-                                   static_cast<__half*>(C), m, n, s),
+                                   static_cast<__half*>(C), m, n, planes),
                 "cudaLaunchKernelEx(splitk_reduce)");
   return BEAM_OK;
 }

@@ -63,6 +63,7 @@ struct GemmParams {
   int hint_b;   // same for the B loads
   int hint_c;   // same for the C stores (GEMM mode)
   int flags;    // BEAM_FLAG_* bits of the call
+  int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
@@ -373,7 +374,27 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4 + 16));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int num_kb = (p.k + S::kBK - 1) / S::kBK;
+  // Folded split-K (M, N <= 64; BN = 128, one CTA): a stage carries TWO k-blocks.  Rows 0..63 of the A box hold
+  // A's rows for k-block 2i and rows 64..127 the same rows for k-block 2i + 1 (likewise B), so one M = 128,
+  // N = 128 UMMA computes [A_2i; A_2i+1] x [B_2i; B_2i+1]^T, whose two diagonal 64 x 64 blocks are the wanted
+  // products (the off-diagonal blocks are ignored).  No shared-memory row is zero fill, and the ring holds twice
+  // as much of K.  The two diagonal blocks leave as two partial slices (2 * slice, 2 * slice + 1).
+  constexpr bool kCanFold = (kMode == kModeSplitK) && BN == 128 && kCta == 1;
+  const bool fold = kCanFold && p.fold != 0;
+  const int num_kb = fold ? ((p.k + S::kBK - 1) / S::kBK + 1) / 2 : (p.k + S::kBK - 1) / S::kBK;
+  auto load_stage = [&](int s, int kb, int row_a, int row_b, uint64_t pol_a_, uint64_t pol_b_) {  // one CTA per tile
+    ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+    if (fold) {
+      const int k0 = 2 * kb * S::kBK;
+      ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), k0, row_a, pol_a_);
+      ptx::tma_load_2d_hint(smem_a(s) + S::kABytes / 2, &p.tm_a, full_bar(s), k0 + S::kBK, row_a, pol_a_);
+      ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), k0, row_b, pol_b_);
+      ptx::tma_load_2d_hint(smem_b(s) + S::kBBytes / 2, &p.tm_b, full_bar(s), k0 + S::kBK, row_b, pol_b_);
+    } else {
+      ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, pol_a_);
+      ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b_);
+    }
+  };
   uint32_t preloaded = 0;  // k-blocks of the first work item that thread 0 put in flight during set-up
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -408,10 +429,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         const int row_a = w0.mt * S::kBM;
         const int row_b = w0.nt * BN;
         for (int kb = w0.kb0; kb < w0.kb1 && preloaded < static_cast<uint32_t>(kStages); ++kb, ++preloaded) {
-          const int s = static_cast<int>(preloaded);
-          ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-          ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, ptx::l2_policy(p.hint_a));
-          ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, ptx::l2_policy(p.hint_b));
+          load_stage(static_cast<int>(preloaded), kb, row_a, row_b, ptx::l2_policy(p.hint_a),
+                     ptx::l2_policy(p.hint_b));
         }
         BEAM_STAMP(2);
       }
@@ -458,9 +477,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             break;
           }
           if constexpr (kCta == 1) {
-            ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-            ptx::tma_load_2d_hint(smem_a(s), &p.tm_a, full_bar(s), kb * S::kBK, row_a, pol_a);
-            ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b);
+            load_stage(s, kb, row_a, row_b, pol_a, pol_b);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
@@ -595,7 +612,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
       constexpr int kChunkCols = (kMode == kModeGemm) ? 64 : 32;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += kChunkCols) {
+      // Folded split-K: lanes 0..63 own the block in TMEM columns 0..63, lanes 64..127 the one in columns 64..127.
+      const int fold_half = fold ? static_cast<int>(quad >> 1) : 0;
+      const int c_begin = fold ? fold_half * 64 : 0;
+      const int c_end = fold ? c_begin + 64 : BN;
+      for (int c = c_begin; c < c_end; c += kChunkCols) {
         uint32_t out[32];  // this row's 128 bytes of the chunk
         if constexpr (kMode == kModeGemm) {
           uint32_t v0[32], v1[32];
@@ -629,7 +650,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             }
           }
         }
-        bool box_live = col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m;  // warp-uniform
+        // where the box goes: (x, y) in C / scratch coordinates, z = scratch plane
+        const int box_x = fold ? c - c_begin : col0 + c;
+        const int box_y = fold ? static_cast<int>(quad & 1u) * 32 : row0 + static_cast<int>(quad) * 32;
+        const int box_z = fold ? 2 * w.slice + fold_half : w.slice;
+        bool box_live = box_x < p.n && box_y < p.m;  // warp-uniform
 #ifdef BEAM_TRACE
         if (p.debug & 1) box_live = false;
 #endif
@@ -652,9 +677,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           __syncwarp();
           if (lane == 0) {
             if constexpr (kMode == kModeGemm) {
-              store_c_box(p, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
+              store_c_box(p, buf, box_x, box_y);
             } else {
-              ptx::tma_store_3d(&p.tm_s, buf, col0 + c, row0 + static_cast<int>(quad) * 32, w.slice);
+              ptx::tma_store_3d(&p.tm_s, buf, box_x, box_y, box_z);
               ptx::tma_store_commit();
             }
           }

@@ -110,6 +110,7 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.hint_c = 0;
   p.n_peers = 0;
   p.flags = 0;
+  p.fold = 0;
   p.status = fault_word;
 #ifdef BEAM_TRACE
   p.trace = nullptr;

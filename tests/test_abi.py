@@ -94,7 +94,9 @@ def test_splitk_sizing_functions(lib):
     ws.restype = ctypes.c_size_t
     ws.argtypes = [i, i, i, i, i]
     assert ws(128, 256, 65536, 128, 64) == 64 * 128 * 256 * 4
-    assert ws(64, 64, 131072, 64, 16) == 16 * 64 * 64 * 4
+    # problems with M, N <= 64 run folded (two k-blocks per UMMA): every slice leaves two partial planes
+    assert ws(64, 64, 131072, 64, 16) == 2 * 16 * 64 * 64 * 4
+    assert ws(64, 64, 131072, 128, 16) == 16 * 64 * 64 * 4        # an explicit 128-wide tile does not fold
     assert ws(0, 64, 64, 0, 0) == 0
     h = lib.beam_gemmrc_splitk_heuristic
     h.argtypes = [i, i, i, i]
@@ -103,7 +105,7 @@ def test_splitk_sizing_functions(lib):
     assert h(8192, 8192, 8192, 0) == 1                    # a large-MN problem is not split
     assert h(64, 64, 256, 64) == 1                        # too little K to split
     # a split factor beyond K/64 falls back to the heuristic
-    assert ws(64, 64, 128, 64, 50) == h(64, 64, 128, 64) * 64 * 64 * 4
+    assert ws(64, 64, 128, 64, 50) == 2 * h(64, 64, 128, 64) * 64 * 64 * 4
     ln = lib.beam_gemmrc_layernorm_workspace_bytes
     ln.restype = ctypes.c_size_t
     ln.argtypes = [i, i, i]
