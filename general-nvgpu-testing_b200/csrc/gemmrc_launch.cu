@@ -328,6 +328,7 @@ int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
     (void)cudaGetLastError();
   }
   long long s = sms / (tiles > 0 ? tiles : 1);
+  if (splitk_folds(m, n, tile_n)) s = (s + 1) / 2;  // a folded slice leaves two planes: half as many slices reduce as fast
   if (flags & BEAM_FLAG_INPUTS_STABLE) {
     // every N tile re-reads its rows of A, every M tile its rows of B (from L2 after the first reader)
     const double bytes = 2.0 * k * (static_cast<double>(m) * n_tiles + static_cast<double>(n) * m_tiles);
