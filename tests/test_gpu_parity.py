@@ -101,6 +101,52 @@ def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     _healthy(beam)
 
 
+def test_random_shapes_all_paths(beam, oracle_mod):
+    """Seeded sweep of awkward shapes through the large-GEMM tile families, split-K and the fused LayerNorm."""
+    rng = np.random.Generator(np.random.PCG64(2024))
+    for trial in range(16):
+        m = int(rng.integers(1, 700))
+        n = int(rng.integers(1, 90)) * 8
+        k = int(rng.integers(1, 160)) * 8
+        a, b = _inputs(m, n, k, "uniform", 9000 + trial)
+        want = oracle_mod.gemmrc(a, b)
+        da, db = _dev(a), _dev(b)
+        tile_n, cta_pair = [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2), (512, 2)][trial % 6]
+        c = torch.full((m, n), -3.0, dtype=torch.float16, device="cuda")
+        beam.gemmrc(da, db, c, tile_n=tile_n, cta_pair=cta_pair)
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL, (m, n, k, tile_n, cta_pair)
+        c.fill_(-3.0)
+        beam.cutlass_gemmrc_splitk(da, db, c, split_k_slices=int(rng.integers(0, 6)))
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL, ("splitk", m, n, k)
+        gamma = (1 + 0.1 * rng.standard_normal(n)).astype(np.float16)
+        beta = (0.1 * rng.standard_normal(n)).astype(np.float16)
+        if n >= 16:  # LayerNorm over a handful of columns is dominated by fp16 rounding of gamma/beta, not by the kernel
+            beam.cutlass_parallel_gemmrc_lnr(da, db, c, _dev(gamma), _dev(beta), 1e-5)
+            ln = oracle_mod.gemm_layernorm(a, b, gamma, beta, 1e-5)
+            assert oracle_mod.floored_max_rel(c.cpu().numpy(), ln) <= oracle_mod.REL_TOL, ("layernorm", m, n, k)
+    _healthy(beam)
+
+
+def test_two_streams_reentrant(beam, oracle_mod):
+    """Calls on different streams do not share state: each gets its own result (device-pointer entry points take the
+    caller's stream and keep nothing between calls)."""
+    cases = []
+    for i in range(4):
+        a, b = _inputs(512 + 64 * i, 768, 1024, 0.1, 600 + i)
+        cases.append((_dev(a), _dev(b), oracle_mod.gemmrc(a, b),
+                      torch.zeros(512 + 64 * i, 768, dtype=torch.float16, device="cuda")))
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for i, (da, db, _, c) in enumerate(cases):
+            with torch.cuda.stream(streams[i % 2]):
+                beam.cutlass_gemmrc(da, db, c)
+    torch.cuda.synchronize()
+    for _, _, want, c in cases:
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    _healthy(beam)
+
+
 def test_zero_and_identity_inputs(beam):
     n = 384
     eye = torch.eye(n, dtype=torch.float16, device="cuda")
