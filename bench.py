@@ -250,6 +250,14 @@ def extras(beam, torch, a, b, c, peaks):
             "cublas_us": graph_us([(lambda i=i: torch.matmul(As[i % sets], Bs[i % sets].t(), out=cc))
                                    for i in range(24)])}
         del As, Bs
+    # GEMM with a co-scheduled element-wise SiLU over a second tensor (what the reference's cute_gemm_ln.cu does)
+    xs = torch.randn(64 << 20, device="cuda", dtype=torch.float16)
+    ys = torch.empty_like(xs)
+    out["gemm_8192_plus_silu_64Mi"] = {
+        "fused_ms": ev_time(lambda: beam.cutlass_parallel_gemmrc_silu(a, b, c, xs, ys), 10),
+        "gemm_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]), 10),
+        "torch_silu_ms": ev_time(lambda: torch.nn.functional.silu(xs, inplace=False), 10)}
+    del xs, ys
     out["reference_kernels_sm80_on_b200"] = reference_kernels(torch, a, b, c, ev_time)
     m, n, k = 16384, 4096, 4096
     x = (torch.randn(m, k, device="cuda") * 0.02).half()

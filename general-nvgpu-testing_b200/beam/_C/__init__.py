@@ -26,6 +26,7 @@ __all__ = [
     "custom_gemmrc_128x128",
     "custom_gemmrc_128x256",
     "cutlass_parallel_gemmrc_lnr",
+    "cutlass_parallel_gemmrc_silu",
     "gemmrc",
     "gemmrc_host",
     "gemmrc_allgather",
@@ -92,6 +93,7 @@ def _load():
     L.beam_gemmrc_layernorm_workspace_bytes.argtypes = [i, i, i]
     L.beam_gemmrc_layernorm.argtypes = [vp, vp, vp, vp, vp, f, i, i, i, vp, sz, vp]
     L.beam_gemmrc_fp16_host.argtypes = [vp, vp, vp, i, i, i]
+    L.beam_gemmrc_silu.argtypes = [vp, vp, vp, i, i, i, vp, vp, ctypes.c_longlong, vp]
     L.beam_gemmrc_fp16_allgather.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp]
     _lib = L
     return L
@@ -260,6 +262,24 @@ def cutlass_parallel_gemmrc_lnr(a, b, c, gamma, beta, eps=1e-5):
                                      float(eps), m, n, k, ws.data_ptr(), ws.numel(), _stream(a))
     if st != BEAM_OK:
         _raise(st, "beam_gemmrc_layernorm")
+
+
+def cutlass_parallel_gemmrc_silu(a, b, c, x, y):
+    """c = a @ b.T and, in the same kernel, y = silu(x) element-wise over a second fp16 tensor: the semantics of the
+    reference kernel registered as `cutlass_parallel_gemmrc_lnr` (cuda/cute_kernels/main.cc:55-76, cute_gemm_ln.cu),
+    which co-schedules a memory-bound element-wise op with a compute-bound GEMM."""
+    m, n, k = _check_abc(a, b, c)
+    for name, t in (("x", x), ("y", y)):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous() and t.dtype == torch.float16):
+            raise TypeError("%s must be a contiguous CUDA float16 tensor" % name)
+    if x.numel() != y.numel():
+        raise ValueError("x and y must have the same number of elements")
+    L = _load()
+    with torch.cuda.device(a.device):
+        st = L.beam_gemmrc_silu(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, x.data_ptr(), y.data_ptr(),
+                                x.numel(), _stream(a))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_silu")
 
 
 def gemmrc_allgather(a_local, b, gathered_ptrs, rank, n, tile_n=0, cta_pair=0, stages=0, group_m=0):

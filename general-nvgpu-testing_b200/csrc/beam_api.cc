@@ -161,6 +161,11 @@ int beam_gemmrc_layernorm(const void* X, const void* W, void* out, const void* g
                                static_cast<cudaStream_t>(stream));
 }
 
+int beam_gemmrc_silu(const void* A, const void* B, void* C, int m, int n, int k, const void* x, void* y,
+                     long long count, void* stream) {
+  return launch_gemm_silu(A, B, C, m, n, k, x, y, count, static_cast<cudaStream_t>(stream));
+}
+
 int beam_gemmrc_fp16_host(const void* A_host, const void* B_host, void* C_host, int m, int n, int k) {
   return gemmrc_from_host(A_host, B_host, C_host, m, n, k);
 }

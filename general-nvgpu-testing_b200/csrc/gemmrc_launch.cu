@@ -30,6 +30,9 @@ struct ExtraArgs {
   int l2_hints = 0;
   int flags = 0;
   int fold = 0;
+  const __half* ew_in = nullptr;
+  __half* ew_out = nullptr;
+  long long ew_count = 0;
   const void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // fused all-gather
   int n_peers = 0;
   float2* row_part = nullptr;
@@ -81,7 +84,10 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
                       fold ? S::kBRows / 2 : S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
   p.fold = fold ? 1 : 0;
-  if (kMode == kModeGemm) {
+  p.ew_in = ex.ew_in;
+  p.ew_out = ex.ew_out;
+  p.ew_count = ex.ew_count;
+  if (kMode == kModeGemm || kMode == kModeGemmSilu) {
     st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n),
                         32, 64, true);
   } else {
@@ -299,6 +305,25 @@ int launch_gemmrc_allgather(const void* A, const void* B, void* const* gathered,
       ex.peer_c[ex.n_peers++] = block;
   }
   return launch_gemmrc_ex(A, B, local, m, n, k, plan, ex, stream);
+}
+
+// ------------------------------------------------------------------- GEMM with a co-scheduled SiLU
+int launch_gemm_silu(const void* A, const void* B, void* C, int m, int n, int k, const void* x, void* y,
+                     long long count, cudaStream_t stream) {
+  int st = validate_gemm_args(A, B, C, m, n, k);
+  if (st != BEAM_OK) return st;
+  if (count < 0 || (count > 0 && (!x || !y))) return BEAM_ERR_INVALID_ARG;
+  if (count > 0 && (!aligned16(x) || !aligned16(y))) return BEAM_ERR_ALIGNMENT;
+  DeviceCtx* ctx = current_device_ctx(&st);
+  if (!ctx) return st;
+  ExtraArgs ex;
+  ex.ew_in = static_cast<const __half*>(x);
+  ex.ew_out = static_cast<__half*>(y);
+  ex.ew_count = count;
+  const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+  if (pair_tiles >= ctx->sm_count / 2)
+    return launch_instance<256, 6, 2, kModeGemmSilu>(ctx, A, B, C, m, n, k, 0, 0, ex, stream);
+  return launch_instance<128, 6, 1, kModeGemmSilu>(ctx, A, B, C, m, n, k, 0, 0, ex, stream);
 }
 
 // ---------------------------------------------------------------------------------- split-K

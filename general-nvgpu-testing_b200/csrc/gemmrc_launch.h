@@ -18,6 +18,9 @@ int default_stages(int tile_n, int cta_pair);
 int validate_gemm_args(const void* A, const void* B, const void* C, int m, int n, int k);
 int launch_gemmrc(const void* A, const void* B, void* C, int m, int n, int k, const GemmPlan& plan,
                   cudaStream_t stream);
+// GEMM plus an independent y = silu(x) over `count` halves worked in by the epilogue warps.
+int launch_gemm_silu(const void* A, const void* B, void* C, int m, int n, int k, const void* x, void* y,
+                     long long count, cudaStream_t stream);
 // Fused GEMM + all-gather: C of this rank's m rows goes to row block `rank` of every gathered[d] (d < world).
 int launch_gemmrc_allgather(const void* A, const void* B, void* const* gathered, int world, int rank, int m, int n,
                             int k, const GemmPlan& plan, cudaStream_t stream);

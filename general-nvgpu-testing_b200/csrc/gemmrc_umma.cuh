@@ -23,6 +23,9 @@
 //   kModeGemm       fp32 -> fp16, store C.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
+//   kModeGemmSilu   the GEMM epilogue, plus an unrelated element-wise y = x / (1 + exp(-x)) over a second tensor
+//                   that the epilogue warps work through, 1024 elements at a time, while they wait for their
+//                   next accumulator (what the reference's cute_gemm_ln.cu co-schedules on a quarter of its CTAs).
 //   kModeLayerNorm  tiles are walked in GEMM order (so A and B stay L2-resident).  Each tile's epilogue
 //                   parks its fp32 values in a scratch panel, writes one (mean, M2) pair per row for
 //                   its N range, and takes a ticket for its 128-row panel.  The CTA that draws the last
@@ -36,7 +39,7 @@
 
 namespace beam {
 
-enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2 };
+enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3 };
 
 struct GemmParams {
   CUtensorMap tm_a;  // A  [M, K], box 128 x 64, 128 B swizzle
@@ -63,6 +66,9 @@ struct GemmParams {
   int hint_b;   // same for the B loads
   int hint_c;   // same for the C stores (GEMM mode)
   int flags;    // BEAM_FLAG_* bits of the call
+  const __half* ew_in;   // kModeGemmSilu: element-wise input, ew_count halves
+  __half* ew_out;        // kModeGemmSilu: element-wise output
+  long long ew_count;
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int* status;  // device fault word
 #ifdef BEAM_TRACE
@@ -175,6 +181,37 @@ __device__ __forceinline__ void store_c_box(const GemmParams& p, uint32_t buf, i
   ptx::tma_store_2d_hint(&p.tm_c, buf, x, y, ptx::l2_policy(p.hint_c));
   for (int d = 0; d < p.n_peers; ++d) ptx::tma_store_2d(&p.tm_peer[d], buf, x, y);
   ptx::tma_store_commit();
+}
+
+// One warp applies y = x / (1 + exp(-x)) (fp32 math, fp16 in and out; cute_gemm_ln.cu:181-198 of the reference) to
+// chunk `chunk` of 1024 elements: four coalesced 16-byte loads per lane in flight, then four stores.
+__device__ __forceinline__ void silu_chunk(const GemmParams& p, long long chunk, uint32_t lane) {
+  const long long base = chunk * 1024;
+  uint4 v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long e = base + (static_cast<long long>(i) * 32 + lane) * 8;
+    v[i] = make_uint4(0, 0, 0, 0);
+    if (e + 8 <= p.ew_count) v[i] = *reinterpret_cast<const uint4*>(p.ew_in + e);  // plain load: x may alias y
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long e = base + (static_cast<long long>(i) * 32 + lane) * 8;
+    if (e + 8 <= p.ew_count) {
+      __half2* h = reinterpret_cast<__half2*>(&v[i]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 x = __half22float2(h[q]);
+        h[q] = __floats2half2_rn(x.x / (1.f + __expf(-x.x)), x.y / (1.f + __expf(-x.y)));
+      }
+      *reinterpret_cast<uint4*>(p.ew_out + e) = v[i];
+    } else if (e < p.ew_count) {  // the ragged last few elements, one at a time
+      for (long long t = e; t < p.ew_count; ++t) {
+        const float x = __half2float(p.ew_in[t]);
+        p.ew_out[t] = __float2half_rn(x / (1.f + __expf(-x)));
+      }
+    }
+  }
 }
 
 // Chan's parallel update of (count, mean, M2) with a block of `nb` values whose own mean and M2 are given.
@@ -548,6 +585,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const uint32_t row_in_tile = quad * 32u + lane;
     const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
     uint32_t store_count = 0;  // bulk stores this warp has issued (selects the staging buffer)
+    // kModeGemmSilu: chunks of the element-wise tensor are dealt round-robin to the grid's epilogue warps
+    const long long ew_chunks = (kMode == kModeGemmSilu) ? (p.ew_count + 1023) / 1024 : 0;
+    const long long ew_stride = static_cast<long long>(gridDim.x) * 4;
+    long long ew_chunk = static_cast<long long>(blockIdx.x) * 4 + quad;
     if constexpr (kMode == kModeSplitK) ptx::grid_dependency_wait();  // before this thread's first global write
     int ln_pending = -1;                               // LayerNorm: a unit this warp claimed ahead of its publication
     uint32_t ln_ring_count = 0;                        // LayerNorm: boxes this warp's landing ring has received
@@ -559,7 +600,37 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // Lane 0 polls (with back-off) for the whole warp, which stays converged for the .sync.aligned TMEM
       // loads below.
       bool ready;
-      if constexpr (kMode == kModeLayerNorm) {
+      if constexpr (kMode == kModeGemmSilu) {
+        // While the accumulator is not ready, this warp works through its share of the element-wise tensor.
+        const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
+        for (;;) {
+          int hit = 0;
+          if (lane == 0) hit = ptx::mbar_try_wait(tmem_full_bar(acc), acc_ph) ? 1 : 0;
+          hit = __shfl_sync(0xffffffffu, hit, 0);
+          if (hit) {
+            ready = true;
+            break;
+          }
+          if (ew_chunk < ew_chunks) {
+            silu_chunk(p, ew_chunk, lane);
+            ew_chunk += ew_stride;
+          } else {
+            __nanosleep(128);
+            int give_up = 0;
+            if (lane == 0) {
+              if (!*cta_abort && ptx::globaltimer_ns() > deadline) {
+                *cta_abort = 1;
+                if (p.status) atomicCAS(p.status, 0, static_cast<int>(kFaultEpilogueWait));
+              }
+              give_up = *cta_abort;
+            }
+            if (__shfl_sync(0xffffffffu, give_up, 0)) {
+              ready = false;
+              break;
+            }
+          }
+        }
+      } else if constexpr (kMode == kModeLayerNorm) {
         // While the accumulator is not ready, this warp spends the time on the second pass: one unit of a
         // published panel per iteration (its staging buffers are idle: its stores have completed).
         BEAM_ACC_BEGIN();
@@ -610,7 +681,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
       float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm: this row's statistics over this tile
       // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
-      constexpr int kChunkCols = (kMode == kModeGemm) ? 64 : 32;
+      constexpr bool kHalfOut = (kMode == kModeGemm || kMode == kModeGemmSilu);  // fp16 C through tm_c
+      constexpr int kChunkCols = kHalfOut ? 64 : 32;
 #pragma unroll 1
       // Folded split-K: lanes 0..63 own the block in TMEM columns 0..63, lanes 64..127 the one in columns 64..127.
       const int fold_half = fold ? static_cast<int>(quad >> 1) : 0;
@@ -618,7 +690,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const int c_end = fold ? c_begin + 64 : BN;
       for (int c = c_begin; c < c_end; c += kChunkCols) {
         uint32_t out[32];  // this row's 128 bytes of the chunk
-        if constexpr (kMode == kModeGemm) {
+        if constexpr (kHalfOut) {
           uint32_t v0[32], v1[32];
           ptx::tmem_ld_32x32(taddr + c, v0);
           ptx::tmem_ld_32x32(taddr + c + 32, v1);
@@ -676,7 +748,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if constexpr (kMode == kModeGemm) {
+            if constexpr (kHalfOut) {
               store_c_box(p, buf, box_x, box_y);
             } else {
               ptx::tma_store_3d(&p.tm_s, buf, box_x, box_y, box_z);
@@ -717,6 +789,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         }
         BEAM_ACC_END(10);
       }
+    }
+    if constexpr (kMode == kModeGemmSilu) {
+      for (; ew_chunk < ew_chunks; ew_chunk += ew_stride) silu_chunk(p, ew_chunk, lane);
     }
     if constexpr (kMode == kModeLayerNorm) {
       // No tiles left: keep normalising until every unit of the problem has been claimed and this warp's own

@@ -111,6 +111,9 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.n_peers = 0;
   p.flags = 0;
   p.fold = 0;
+  p.ew_in = nullptr;
+  p.ew_out = nullptr;
+  p.ew_count = 0;
   p.status = fault_word;
 #ifdef BEAM_TRACE
   p.trace = nullptr;

@@ -184,6 +184,16 @@ BEAM_API size_t beam_gemmrc_layernorm_workspace_bytes(int m, int n, int k);
 BEAM_API int beam_gemmrc_layernorm(const void* X, const void* W, void* out, const void* gamma, const void* beta, float eps,
                           int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- GEMM with a co-scheduled element-wise SiLU ------------------------------------------------- */
+
+/* What the reference kernel behind `cutlass_parallel_gemmrc_lnr` really computes (cuda/cute_kernels/
+ * cute_gemm_ln.cu:24-245, entry :230-245): C = A x B^T and, independently, y[i] = x[i] / (1 + exp(-x[i])) for
+ * `count` halves of a second tensor (fp32 math, fp16 in and out).  The reference parks the element-wise work on
+ * a quarter of its CTAs; here the epilogue warps of the persistent GEMM work through it, 1024 elements at a time,
+ * while they wait for their next accumulator.  x, y: 16-byte aligned device pointers; x may equal y. */
+BEAM_API int beam_gemmrc_silu(const void* A, const void* B, void* C, int m, int n, int k, const void* x, void* y,
+                              long long count, void* stream);
+
 /* ---- host-buffer convenience (what a caller with pageable or pinned HOST arrays uses) ---------- */
 
 /* A, B, C are HOST pointers. Copies A and B to the device in row blocks, runs beam_cutlass_gemmrc on

@@ -99,6 +99,20 @@ def test_operator_and_tuner_interface():
     assert tuner.tune([4, 4, 4]) == ("op", 1.0)                          # cache hit needs no GPU
 
 
+def test_driver_check_verdicts():
+    """gemm_test.check keeps the reference's rule: rtol = atol = 2e-2, fewer than 0.12 % mismatches only warn."""
+    import gemm_test
+    want = torch.ones(100, 100, dtype=torch.float16)
+    got = want.clone()
+    assert gemm_test.check(lambda: None, [want], [got]) == "success"
+    got[0, 0] = 2.0                                   # 1 of 10000 = 0.01 %
+    assert gemm_test.check(lambda: None, [want], [got]) == "warning"
+    got[:1, :20] = 2.0                                # 0.2 %
+    assert gemm_test.check(lambda: None, [want], [got]) == "failure"
+    got = want + 0.03                                 # inside atol + rtol * |c| = 0.04
+    assert gemm_test.check(lambda: None, [want], [got]) == "success"
+
+
 def test_tuner_cache_persistence(tmp_path):
     import beam
     path = str(tmp_path / "tuned.json")
