@@ -111,13 +111,13 @@ def _raise(status, what):
     raise BeamError(msg)
 
 
-def _check_abc(a, b, c):
+def _check_abc(a, b, c, allow_bf16=False):
     """Same preconditions as the reference's checkTensor / checkIntEqual / fp16 dispatch
     (cuda/include/torch_utils.h:7-47, cuda/cutlass_kernels/main.cc:25-45), reported as exceptions."""
     for name, t in (("a", a), ("b", b), ("c", c)):
         if not isinstance(t, torch.Tensor):
             raise TypeError("%s must be a torch.Tensor" % name)
-        if t.dtype != torch.float16:
+        if t.dtype != torch.float16 and not (allow_bf16 and t.dtype == torch.bfloat16 and t.dtype == a.dtype):
             raise TypeError("%s must be float16, got %s" % (name, t.dtype))
         if not t.is_cuda:
             raise ValueError("%s must be a CUDA tensor (there is no CPU path)" % name)
@@ -195,9 +195,13 @@ def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 6
 
 
 def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0):
-    """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over."""
-    m, n, k = _check_abc(a, b, c)
-    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), 0)
+    """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over.  The three tensors may
+    be bfloat16 instead of float16 (all three alike)."""
+    m, n, k = _check_abc(a, b, c, allow_bf16=True)
+    if not (a.dtype == b.dtype == c.dtype):
+        raise TypeError("a, b, c must share one dtype")
+    flags = 2 if a.dtype == torch.bfloat16 else 0
+    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), flags)
     L = _load()
     with torch.cuda.device(a.device):
         st = L.beam_gemmrc_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg), _stream(a))

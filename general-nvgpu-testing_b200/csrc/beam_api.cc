@@ -52,6 +52,8 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.group_m = cfg->group_m;
     plan.max_ctas = cfg->max_ctas;
     plan.l2_hints = cfg->l2_hints;
+    plan.bf16 = (cfg->flags & BEAM_FLAG_BF16) ? 1 : 0;
+    if (cfg->flags & ~(BEAM_FLAG_BF16)) return BEAM_ERR_INVALID_ARG;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
     if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0 || plan.l2_hints < 0 || plan.l2_hints > 222)
       return BEAM_ERR_INVALID_ARG;

@@ -30,6 +30,7 @@ struct ExtraArgs {
   int l2_hints = 0;
   int flags = 0;
   int fold = 0;
+  int bf16 = 0;
   const __half* ew_in = nullptr;
   __half* ew_out = nullptr;
   long long ew_count = 0;
@@ -84,6 +85,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
                       fold ? S::kBRows / 2 : S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
   p.fold = fold ? 1 : 0;
+  p.bf16 = (kMode == kModeGemm) ? ex.bf16 : 0;
   p.ew_in = ex.ew_in;
   p.ew_out = ex.ew_out;
   p.ew_count = ex.ew_count;
@@ -189,6 +191,7 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
     if (st != BEAM_OK) return st;
   }
   p.n_peers = ex.n_peers;
+  p.bf16 = ex.bf16;
   p.c = static_cast<__half*>(C);
   p.m = m;
   p.n = n;
@@ -255,6 +258,7 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   if (!ctx) return st;
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
+  ex.bf16 = plan.bf16;
   if (plan.tile_n == 512) {
     if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
     if (plan.stages == 0 || plan.stages == 4)

@@ -11,6 +11,7 @@ struct GemmPlan {
   int stages = 0;     // 0 = deepest ring that fits
   int group_m = 0;    // 0 = default rasterisation group
   int max_ctas = 0;   // 0 = whole device
+  int bf16 = 0;       // operands and result are bf16 instead of fp16
   int l2_hints = 0;   // decimal digits: tens = A loads, ones = B loads; 0 normal, 1 evict-first, 2 evict-last
 };
 

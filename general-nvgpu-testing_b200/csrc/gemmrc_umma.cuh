@@ -69,6 +69,7 @@ struct GemmParams {
   const __half* ew_in;   // kModeGemmSilu: element-wise input, ew_count halves
   __half* ew_out;        // kModeGemmSilu: element-wise output
   long long ew_count;
+  int bf16;     // GEMM mode: A, B, C are bf16 instead of fp16 (same kernels: descriptor bits and final rounding)
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int* status;  // device fault word
 #ifdef BEAM_TRACE
@@ -528,7 +529,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, BN);
+      const uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, BN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       uint32_t it = 0;
       bool alive = true;
       WorkItem w;
@@ -697,8 +698,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            out[q] = ptx::pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
-            out[16 + q] = ptx::pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+            out[q] = ptx::pack_out2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]), p.bf16);
+            out[16 + q] = ptx::pack_out2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]), p.bf16);
           }
         } else {
           ptx::tmem_ld_32x32(taddr + c, out);

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kHalfN);
+      const uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kHalfN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       uint32_t it = 0;
       bool alive = true;
       WorkItem w;
@@ -218,8 +218,8 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            out[q] = ptx::pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
-            out[16 + q] = ptx::pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+            out[q] = ptx::pack_out2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]), p.bf16);
+            out[16 + q] = ptx::pack_out2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]), p.bf16);
           }
           if (col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m) {
             constexpr uint32_t kBufs = S::kBufsPerWarp;

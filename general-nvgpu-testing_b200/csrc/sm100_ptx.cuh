@@ -302,12 +302,23 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor, kind::f16: fp16 A and B, both K-major, fp32 D, shape M x N.
-//   [4,6) D format 1=f32   [7,10) A format 0=f16   [10,13) B format 0=f16
+//   [4,6) D format 1=f32   [7,10) A format 0=f16, 1=bf16   [10,13) B format 0=f16, 1=bf16
 //   [15] A major 0=K   [16] B major 0=K   [17,23) N>>3   [24,29) M>>4
 __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// Two fp32 values rounded to nearest even and packed as bf16 (bf16 != 0) or fp16.
+__device__ __forceinline__ uint32_t pack_out2(float lo, float hi, int bf16) {
+  if (bf16) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+constexpr uint32_t kIdescBf16Inputs = (1u << 7) | (1u << 10);  // OR into the descriptor for bf16 A and B
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);

@@ -111,6 +111,7 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.n_peers = 0;
   p.flags = 0;
   p.fold = 0;
+  p.bf16 = 0;
   p.ew_in = nullptr;
   p.ew_out = nullptr;
   p.ew_count = 0;

@@ -66,6 +66,9 @@ typedef struct beam_gemm_cfg {
  * (typically the previous split-K call's reduction) is still finishing, and only its writes wait for that
  * kernel to complete.  Without the flag it waits before its first global read, which is always safe. */
 #define BEAM_FLAG_INPUTS_STABLE 1
+/* beam_gemmrc_fp16 only: A, B and C hold bf16 instead of fp16 (same kernels; fp32 accumulation, one rounding to
+ * bf16).  The reference reaches bf16 only through its cuBLAS comparator (cuda/cublas.cc:106-108). */
+#define BEAM_FLAG_BF16 2
 
 BEAM_API const char* beam_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */

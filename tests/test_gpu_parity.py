@@ -403,6 +403,26 @@ def test_gemm_with_coscheduled_silu(beam, oracle_mod, m, n, k, count):
         assert oracle_mod.floored_max_rel(y.cpu().numpy(), y_ref.view(-1).cpu().numpy()) <= 2e-3
 
 
+@pytest.mark.parametrize("tile_n,cta_pair", [(128, 1), (256, 2), (512, 2)])
+def test_bf16_gemm(beam, tile_n, cta_pair):
+    """bf16 operands through the same kernels (descriptor bits + final rounding): against an fp32 matmul of the same
+    bf16 values.  Half an ulp of bf16 is 2^-9 = 2e-3, so the fp16 bound of 1e-2 still holds."""
+    import oracle
+    g = torch.Generator(device="cuda").manual_seed(31)
+    a = (torch.randn(520, 1096, device="cuda", generator=g) * 0.1).bfloat16()
+    b = (torch.randn(776, 1096, device="cuda", generator=g) * 0.1).bfloat16()
+    c = torch.zeros(520, 776, dtype=torch.bfloat16, device="cuda")
+    beam.gemmrc(a, b, c, tile_n=tile_n, cta_pair=cta_pair)
+    want = (a.float() @ b.float().t())
+    assert oracle.floored_max_rel(c.float().cpu().numpy(), want.cpu().numpy()) <= oracle.REL_TOL
+    assert torch.equal(c, torch.matmul(a, b.t())) or \
+        oracle.floored_max_rel(c.float().cpu().numpy(), torch.matmul(a, b.t()).float().cpu().numpy()) <= 8e-3
+    with pytest.raises(TypeError):
+        beam.gemmrc(a, b.half(), c)
+    with pytest.raises(TypeError):
+        beam.cutlass_gemmrc(a, b, c)            # the registry names stay fp16-only, like the reference's
+
+
 def test_reference_style_driver(beam):
     """The driver with the reference's interface (gemm_test.py): every kernel it lists passes its check."""
     import gemm_test
