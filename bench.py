@@ -32,8 +32,8 @@ M_PER_GPU, N, K = 8192, 8192, 8192
 SEED = 1234 + 2
 METRIC = "fp16 gemmrc TFLOP/s (M=8192 per GPU, N=K=8192, fp32 accumulate)"
 UNIT = "TFLOP/s"
-# DRAM bytes per launch of the default kernel at 8192^3 from the committed ncu capture
-# (profiles/gemmrc_256x512_pair_8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
+# DRAM bytes per launch of the default kernel (256x512 pair tile) at 8192^3, from the committed ncu
+# capture of that kernel: dram__bytes_read.sum + dram__bytes_write.sum.
 NCU_DRAM_BYTES_PER_LAUNCH = 1.017210e9 + 1.22840e8
 
 REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",

@@ -14,8 +14,8 @@
 //
 // What it does not do.  It calls no cudaMalloc, cudaFree, or allocating library routine, and it does not use
 // the library's per-device context (whose first use allocates a fault word).  The first call on a device
-// performs a one-time set-up for that device (symbol address lookup, kernel attributes), so make that
-// first call before any stream capture begins on the device.
+// performs a one-time set-up for that device (symbol address lookup, kernel attributes) and is slower than
+// the calls after it.
 //
 // Sharing.  Every call on a device uses the same array and the array keeps whatever the previous call left
 // in it.  Nothing in it has to start at zero: each call's first kernel overwrites every partial element

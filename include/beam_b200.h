@@ -165,8 +165,8 @@ BEAM_API int beam_cutlass_gemmrc_splitk_spec(const void* A, const void* B, void*
  * another allocator at start-up, and for runtimes that forbid allocation after initialisation.
  *   - limit: slices * M * N * 4 bytes <= 16 MiB, otherwise BEAM_ERR_WORKSPACE (use the workspace entry);
  *     the array occupies 16 MiB on every GPU that loads the library until the process exits;
- *   - the first call on a device does a one-time set-up (symbol address, kernel attributes): make it
- *     before any stream capture starts on that device;
+ *   - the first call on a device does a one-time set-up (symbol address, kernel attributes) and is
+ *     therefore slower than the calls after it;
  *   - calls no cudaMalloc / cudaFree / allocating routine and does not touch the library's per-device
  *     context, so beam_device_status() does not see its kernels: pass `device_fault_word` (a zeroed
  *     4-byte device int of your own, or NULL) to receive a DeviceFault code if a bounded wait expires;
