@@ -55,7 +55,7 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.bf16 = (cfg->flags & BEAM_FLAG_BF16) ? 1 : 0;
     if (cfg->flags & ~(BEAM_FLAG_BF16)) return BEAM_ERR_INVALID_ARG;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
-    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < 0 || plan.l2_hints < 0 || plan.l2_hints > 222)
+    if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < -1 || plan.l2_hints < 0 || plan.l2_hints > 333)
       return BEAM_ERR_INVALID_ARG;
   }
   return launch_gemmrc(A, B, C, m, n, k, plan, static_cast<cudaStream_t>(stream));
