@@ -199,7 +199,7 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.ldc = n;
   p.m_tiles = (m + 255) / 256;
   p.n_tiles = (n + S::kTileN - 1) / S::kTileN;
-  p.group_m = group_m > 0 ? group_m : 12;
+  p.group_m = group_m > 0 ? group_m : 16;
   p.slices = 1;
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
@@ -262,10 +262,11 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   ex.bf16 = plan.bf16;
   if (plan.tile_n == 512) {
     if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
-    if (plan.stages == 0 || plan.stages == 4)
-      return launch_wide_instance<4>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
-    if (plan.stages == 3)
+    // Default: the 3-deep ring, which leaves room for two C staging buffers per epilogue warp.
+    if (plan.stages == 0 || plan.stages == 3)
       return launch_wide_instance<3>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+    if (plan.stages == 4)
+      return launch_wide_instance<4>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return BEAM_ERR_UNSUPPORTED;
   }
   BEAM_GEMM_CASE(256, 4, 2)

@@ -9,7 +9,9 @@
 // The price: TMEM (512 columns) holds one tile, so the epilogue cannot hide behind the next tile's main loop
 // by double-buffering.  It hides behind the start of it instead: the first `kStages` k-blocks of a tile are
 // issued half-major (all of half 0, then all of half 1), so the issuer only needs half 0 drained to start
-// and half 1 is drained meanwhile.
+// and half 1 is drained meanwhile.  The drain of half 0 is the exposed part, so the epilogue is made short:
+// eight warps (two per TMEM lane quadrant, 128 columns of each half apiece) pull a whole half into registers
+// and hand it back before rounding or storing anything, so the hand-back does not wait for the C stores.
 #pragma once
 
 #include "gemmrc_umma.cuh"
@@ -29,18 +31,19 @@ struct WideShape {
   static constexpr int kTmemCols = 512;
   static constexpr int kBarBytes = 512;
   static constexpr int kStoreBufBytes = 32 * 128;
-  // A 3-deep ring leaves room for four staging buffers per epilogue warp (stores rarely wait for a buffer);
-  // a 4-deep ring for two.
-  static constexpr int kBufsPerWarp = (kStages <= 3) ? 4 : 2;
-  static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
+  static constexpr int kEpilogueWarps = 8;
+  // A 3-deep ring leaves room for two staging buffers per epilogue warp; a 4-deep ring for one (a warp then
+  // waits for its previous store to have read the buffer, which the TMEM loads and the rounding cover).
+  static constexpr int kBufsPerWarp = (kStages <= 3) ? 2 : 1;
+  static constexpr int kStagingBytes = kEpilogueWarps * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;
-  static constexpr int kThreads = 192;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
-  static_assert((2 * kStages + 3) * 8 + 16 <= kBarBytes, "barrier block too small");
+  static_assert((2 * kStages + 4) * 8 + 16 <= kBarBytes, "barrier block too small");
 };
 
 template <int kStages>
-__global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_kernel(const __grid_constant__ GemmParams p) {
   using S = WideShape<kStages>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5;
@@ -60,10 +63,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
   auto smem_b = [&](int s, int h) { return smem_base + s * S::kStageBytes + S::kABytes + h * S::kBHalfBytes; };
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  const uint32_t tmem_full_bar = bar_base + 8u * (2 * kStages);
-  auto tmem_empty_bar = [&](int h) { return bar_base + 8u * (2 * kStages + 1 + h); };
+  auto tmem_full_bar = [&](int h) { return bar_base + 8u * (2 * kStages + h); };       // one per accumulator half
+  auto tmem_empty_bar = [&](int h) { return bar_base + 8u * (2 * kStages + 2 + h); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
-      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 3));
+      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4));
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
@@ -71,9 +74,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
     }
-    ptx::mbar_init(tmem_full_bar, 1);
-    ptx::mbar_init(tmem_empty_bar(0), 8);  // one arrive per epilogue warp of each CTA
-    ptx::mbar_init(tmem_empty_bar(1), 8);
+    ptx::mbar_init(tmem_full_bar(0), 1);
+    ptx::mbar_init(tmem_full_bar(1), 1);
+    ptx::mbar_init(tmem_empty_bar(0), 2 * S::kEpilogueWarps);  // one arrive per epilogue warp of each CTA
+    ptx::mbar_init(tmem_empty_bar(1), 2 * S::kEpilogueWarps);
     *cta_abort = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&p.tm_a);
@@ -158,6 +162,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
           issue_half(s, 0, g == 0);
         }
         if (!alive) break;
+        if (lead_in == num_kb) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);  // half 0 is complete already
         // half 1 of the same k-blocks; their stages are released here
         {
           BEAM_ACC_BEGIN();
@@ -183,67 +188,98 @@ __global__ void __launch_bounds__(192, 1) gemmrc_wide_kernel(const __grid_consta
           }
           ptx::tc_fence_after();
           issue_half(s, 0, false);
+          // Half 0 completes four UMMAs ahead of half 1: its epilogue starts (and hands the half back) while
+          // half 1 finishes, so the next tile's first UMMAs can queue up right behind this tile's last ones.
+          if (kb == num_kb - 1) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);
           issue_half(s, 1, false);
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
-        if (alive) ptx::umma_commit_pair_both(tmem_full_bar, 0x3);
+        if (alive) ptx::umma_commit_pair_both(tmem_full_bar(1), 0x3);
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
-    const uint32_t quad = warp & 3u;
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const uint32_t quad = warp & 3u;               // TMEM lane quadrant this warp may read
+    const uint32_t col_half = (warp - 2u) >> 2;    // which 128 columns of each accumulator half it drains
+    const uint32_t slot = warp - 2u;
     const uint32_t lead_empty0 = ptx::mapa(tmem_empty_bar(0), 0);
+    const uint32_t lane_base = tmem_base + ((quad * 32u) << 16);
+    // chunk i of a tile: half (i >> 1), columns col_half * 128 + (i & 1) * 64 of that half
+    auto chunk_col = [&](int i) { return (i >> 1) * S::kHalfN + static_cast<int>(col_half) * 128 + (i & 1) * 64; };
     uint32_t store_count = 0;
     WorkItem w;
     for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
       {
         BEAM_ACC_BEGIN();
-        const bool ready = bounded_wait_warp(tmem_full_bar, static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
+        const bool ready = bounded_wait_warp(tmem_full_bar(0), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
                                              kFaultEpilogueWait, lane);
         BEAM_ACC_END(8);
         if (!ready) break;
       }
       BEAM_ACC_BEGIN();
       ptx::tc_fence_after();
-      const int row0 = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
-#pragma unroll 1
-      for (int h = 0; h < 2; ++h) {
-        const int col0 = w.nt * S::kTileN + h * S::kHalfN;
-        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + static_cast<uint32_t>(h) * S::kHalfN;
-#pragma unroll 1
-        for (int c = 0; c < S::kHalfN; c += 64) {
-          uint32_t v0[32], v1[32], out[32];
-          ptx::tmem_ld_32x32(taddr + c, v0);
-          ptx::tmem_ld_32x32(taddr + c + 32, v1);
-          ptx::tmem_ld_wait();
+      const int row0 = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
+      const int tile_col0 = w.nt * S::kTileN;
+      // Both halves are handed back as soon as their accumulators sit in registers, before anything is rounded or
+      // stored: the issuer's wait then depends on TMEM load latency only, not on how fast the (bursty, all CTAs at
+      // once) C stores drain the staging buffers.
+      uint32_t va0[32], va1[32], vb0[32], vb1[32], out[32];
+      auto load_chunk = [&](int i, uint32_t (&lo)[32], uint32_t (&hi)[32]) {
+        ptx::tmem_ld_32x32(lane_base + chunk_col(i), lo);
+        ptx::tmem_ld_32x32(lane_base + chunk_col(i) + 32, hi);
+      };
+      auto round_chunk = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32]) {
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            out[q] = ptx::pack_out2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]), p.bf16);
-            out[16 + q] = ptx::pack_out2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]), p.bf16);
-          }
-          if (col0 + c < p.n && row0 + static_cast<int>(quad) * 32 < p.m) {
-            constexpr uint32_t kBufs = S::kBufsPerWarp;
-            const uint32_t buf = staging_base + (quad * kBufs + (store_count % kBufs)) * S::kStoreBufBytes;
-            if (store_count >= kBufs) {
-              if (lane == 0) ptx::tma_store_wait_read<kBufs - 1>();
-              __syncwarp();
-            }
-            const uint32_t row_addr = buf + lane * 128u;
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj)
-              ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), out[4 * jj],
-                                out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) store_c_box(p, buf, col0 + c, row0 + static_cast<int>(quad) * 32);
-            ++store_count;
-          }
+        for (int q = 0; q < 16; ++q) {
+          out[q] = ptx::pack_out2(__uint_as_float(lo[2 * q]), __uint_as_float(lo[2 * q + 1]), p.bf16);
+          out[16 + q] = ptx::pack_out2(__uint_as_float(hi[2 * q]), __uint_as_float(hi[2 * q + 1]), p.bf16);
         }
-        // this half of the accumulator is drained: the issuer may overwrite it
+      };
+      auto release_half = [&](uint32_t h) {
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * static_cast<uint32_t>(h));
-      }
+        if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * h);
+      };
+      auto stage_and_store = [&](int i) {
+        const int col = tile_col0 + chunk_col(i);
+        if (col < p.n && row0 < p.m) {
+          constexpr uint32_t kBufs = S::kBufsPerWarp;
+          const uint32_t buf = staging_base + (slot * kBufs + (store_count % kBufs)) * S::kStoreBufBytes;
+          if (store_count >= kBufs) {
+            if (lane == 0) ptx::tma_store_wait_read<kBufs - 1>();
+            __syncwarp();
+          }
+          const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj)
+            ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), out[4 * jj],
+                              out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) store_c_box(p, buf, col, row0);
+          ++store_count;
+        }
+      };
+      load_chunk(0, va0, va1);
+      load_chunk(1, vb0, vb1);
+      ptx::tmem_ld_wait();
+      release_half(0);
+      round_chunk(va0, va1);
+      if (!bounded_wait_warp(tmem_full_bar(1), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
+                             kFaultEpilogueWait, lane))
+        break;
+      ptx::tc_fence_after();
+      load_chunk(2, va0, va1);
+      stage_and_store(0);
+      round_chunk(vb0, vb1);
+      load_chunk(3, vb0, vb1);
+      ptx::tmem_ld_wait();
+      release_half(1);
+      stage_and_store(1);
+      round_chunk(va0, va1);
+      stage_and_store(2);
+      round_chunk(vb0, vb1);
+      stage_and_store(3);
       BEAM_ACC_END(9);
     }
   }

@@ -43,9 +43,11 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   }
 }
 
-// The same wait for roles that can afford a slower wake-up (the epilogue, whose accumulator is
-// double-buffered): only lane 0 polls, backing off with nanosleep between polls, and the rest of the warp
-// parks at a warp barrier instead of spinning.  Returns the same value in every lane.
+// The same wait for whole warps (the epilogue, which sleeps through a tile's main loop): only lane 0 waits, suspended
+// in hardware on the barrier for up to kSuspendNs at a time instead of polling, and the rest of the warp parks at
+// the shuffle.  Returns the same value in every lane.
+constexpr uint32_t kSuspendNs = 50000u;
+
 __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, volatile int* cta_abort,
                                                   int* status_word, int fault, uint32_t lane) {
   int ok = 1;
@@ -53,9 +55,8 @@ __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity,
     if (!ptx::mbar_try_wait(bar, parity)) {
       uint64_t t0 = 0;
       for (uint32_t spin = 1;; ++spin) {
-        __nanosleep(128);
-        if (ptx::mbar_try_wait(bar, parity)) break;
-        if ((spin & 0x3FFu) == 0) {
+        if (ptx::mbar_try_wait_suspend(bar, parity, kSuspendNs)) break;
+        if ((spin & 0xFu) == 0) {
           if (*cta_abort) {
             ok = 0;
             break;
