@@ -56,7 +56,8 @@ class beam_gemm_cfg(ctypes.Structure):
         ("max_ctas", ctypes.c_int),
         ("l2_hints", ctypes.c_int),
         ("flags", ctypes.c_int),
-        ("reserved", ctypes.c_int * 2),
+        ("tile_m", ctypes.c_int),
+        ("reserved", ctypes.c_int * 1),
     ]
 
 
@@ -194,14 +195,15 @@ def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 6
     _run("beam_cutlass_gemmrc_spec", a, b, c, tbm, tbn, wm, wn)
 
 
-def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0):
+def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, tile_m=0):
     """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over.  The three tensors may
     be bfloat16 instead of float16 (all three alike)."""
     m, n, k = _check_abc(a, b, c, allow_bf16=True)
     if not (a.dtype == b.dtype == c.dtype):
         raise TypeError("a, b, c must share one dtype")
     flags = 2 if a.dtype == torch.bfloat16 else 0
-    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), flags)
+    cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), flags,
+                        int(tile_m))
     L = _load()
     with torch.cuda.device(a.device):
         st = L.beam_gemmrc_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg), _stream(a))

@@ -108,8 +108,11 @@ class OperatorTuner:
             (128, 1, 4), (128, 1, 6),
         ]
         ret = [Operator(partial(_C.gemmrc, tile_n=tn, cta_pair=cp, stages=st)) for tn, cp, st in search_space]
+        # two-accumulator tiles in the other orientation (512 x 256) and without a persistent grid
+        ret += [Operator(partial(_C.gemmrc, tile_n=256, tile_m=512, cta_pair=2, stages=st)) for st in (3, 4)]
+        ret.append(Operator(partial(_C.gemmrc, tile_n=512, cta_pair=2, stages=3, max_ctas=-1)))
         # The reference's own spelling of the tile families (tuner.py:52-59) stays valid.
-        for tb in ([128, 128], [128, 256], [256, 128], [256, 256], [256, 512]):
+        for tb in ([128, 128], [128, 256], [256, 128], [256, 256], [256, 512], [512, 256]):
             ret.append(Operator(partial(_C.cutlass_gemmrc_spec, shape_threadblock=tb, shape_warp=[64, 64])))
         return ret
 

@@ -53,6 +53,8 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.max_ctas = cfg->max_ctas;
     plan.l2_hints = cfg->l2_hints;
     plan.bf16 = (cfg->flags & BEAM_FLAG_BF16) ? 1 : 0;
+    plan.tile_m = cfg->tile_m;
+    if (plan.tile_m != 0 && plan.tile_m != 512) return BEAM_ERR_INVALID_ARG;
     if (cfg->flags & ~(BEAM_FLAG_BF16)) return BEAM_ERR_INVALID_ARG;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
     if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < -1 || plan.l2_hints < 0 || plan.l2_hints > 333)
@@ -111,7 +113,10 @@ int beam_cutlass_gemmrc_spec(const void* A, const void* B, void* C, int m, int n
     plan.cta_pair = 1;
   else if (tb_m == 256)
     plan.cta_pair = 2;
-  else
+  else if (tb_m == 512 && tb_n == 256) {  // two 256-row accumulators per CTA pair
+    plan.cta_pair = 2;
+    plan.tile_m = 512;
+  } else
     return BEAM_ERR_UNSUPPORTED;
   if (tb_n != 128 && tb_n != 256 && !(tb_n == 512 && tb_m == 256)) return BEAM_ERR_UNSUPPORTED;
   plan.tile_n = tb_n;

@@ -162,11 +162,11 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
 }
 
 // 256 x 512 tiles on CTA pairs (gemmrc_wide.cuh).
-template <int kStages>
+template <int kStages, bool kTall>
 int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
                          int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
   using S = WideShape<kStages>;
-  auto kernel = gemmrc_wide_kernel<kStages>;
+  auto kernel = gemmrc_wide_kernel<kStages, kTall>;
   static int configured_clusters[64] = {0};
   int& resident = configured_clusters[ctx->device];
   if (resident == 0) {
@@ -197,9 +197,9 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.n = n;
   p.k = k;
   p.ldc = n;
-  p.m_tiles = (m + 255) / 256;
-  p.n_tiles = (n + S::kTileN - 1) / S::kTileN;
-  p.group_m = group_m > 0 ? group_m : 16;
+  p.m_tiles = kTall ? (m + 511) / 512 : (m + 255) / 256;
+  p.n_tiles = kTall ? (n + 255) / 256 : (n + S::kTileN - 1) / S::kTileN;
+  p.group_m = group_m > 0 ? group_m : (kTall ? 8 : 16);
   p.slices = 1;
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
@@ -260,13 +260,18 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
   ex.bf16 = plan.bf16;
-  if (plan.tile_n == 512) {
+  if (plan.tile_n == 512 || plan.tile_m == 512) {
+    // two-accumulator tiles: 256 x 512 (tile_n = 512) or 512 x 256 (tile_m = 512, tile_n = 256)
     if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
+    const bool tall = plan.tile_m == 512;
+    if (tall && plan.tile_n != 256) return BEAM_ERR_UNSUPPORTED;
     // Default: the 3-deep ring, which leaves room for two C staging buffers per epilogue warp.
     if (plan.stages == 0 || plan.stages == 3)
-      return launch_wide_instance<3>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+      return tall ? launch_wide_instance<3, true>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream)
+                  : launch_wide_instance<3, false>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     if (plan.stages == 4)
-      return launch_wide_instance<4>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+      return tall ? launch_wide_instance<4, true>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream)
+                  : launch_wide_instance<4, false>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return BEAM_ERR_UNSUPPORTED;
   }
   BEAM_GEMM_CASE(256, 4, 2)

@@ -7,6 +7,7 @@ namespace beam {
 
 struct GemmPlan {
   int tile_n = 256;   // UMMA N
+  int tile_m = 0;     // 0 = 128 rows per CTA; 512 = two 256-row accumulators per CTA pair (with tile_n = 256)
   int cta_pair = 2;   // 1 or 2 CTAs per tile
   int stages = 0;     // 0 = deepest ring that fits
   int group_m = 0;    // 0 = default rasterisation group

@@ -42,7 +42,11 @@ struct WideShape {
   static_assert((2 * kStages + 4) * 8 + 16 <= kBarBytes, "barrier block too small");
 };
 
-template <int kStages>
+// kTall = false: 256 x 512 tile, the two accumulators are the two 256-column halves (one A box, two B boxes
+// per stage).  kTall = true: 512 x 256 tile, the two accumulators are the two 256-row halves (two A boxes, one
+// B box per stage), and inside a k-block the UMMAs alternate between the halves so that consecutive
+// instructions read the same B operand.
+template <int kStages, bool kTall>
 __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_kernel(const __grid_constant__ GemmParams p) {
   using S = WideShape<kStages>;
   extern __shared__ uint8_t smem_raw[];
@@ -59,8 +63,10 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t staging_base = smem_base + kStages * S::kStageBytes;
   const uint32_t bar_base = staging_base + S::kStagingBytes;
-  auto smem_a = [&](int s) { return smem_base + s * S::kStageBytes; };
-  auto smem_b = [&](int s, int h) { return smem_base + s * S::kStageBytes + S::kABytes + h * S::kBHalfBytes; };
+  // a stage is three 16 KB boxes; which of them hold A and B depends on the orientation
+  auto smem_box = [&](int s, int i) { return smem_base + s * S::kStageBytes + i * S::kABytes; };
+  auto smem_a = [&](int s, int h) { return smem_box(s, kTall ? h : 0); };
+  auto smem_b = [&](int s, int h) { return smem_box(s, kTall ? 2 : 1 + h); };
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int h) { return bar_base + 8u * (2 * kStages + h); };       // one per accumulator half
@@ -104,9 +110,11 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       WorkItem w;
       for (int j = 0; alive && work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
-        const int row_a = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
-        const int row_b0 = w.nt * S::kTileN + static_cast<int>(cta_rank) * S::kBRows;
-        const int row_b1 = row_b0 + S::kHalfN;
+        // rows of the three boxes this CTA loads: (A, B half 0, B half 1) or (A half 0, A half 1, B)
+        const int r0 = kTall ? w.mt * 512 + static_cast<int>(cta_rank) * S::kBM
+                             : w.mt * 256 + static_cast<int>(cta_rank) * S::kBM;
+        const int r1 = kTall ? r0 + 256 : w.nt * S::kTileN + static_cast<int>(cta_rank) * S::kBRows;
+        const int r2 = kTall ? w.nt * 256 + static_cast<int>(cta_rank) * S::kBRows : r1 + S::kHalfN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -116,9 +124,10 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           }
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
           const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
-          ptx::tma_load_2d_pair_hint(smem_a(s), &p.tm_a, lead_bar, kb * S::kBK, row_a, pol_a);
-          ptx::tma_load_2d_pair_hint(smem_b(s, 0), &p.tm_b, lead_bar, kb * S::kBK, row_b0, pol_b);
-          ptx::tma_load_2d_pair_hint(smem_b(s, 1), &p.tm_b, lead_bar, kb * S::kBK, row_b1, pol_b);
+          ptx::tma_load_2d_pair_hint(smem_box(s, 0), &p.tm_a, lead_bar, kb * S::kBK, r0, pol_a);
+          ptx::tma_load_2d_pair_hint(smem_box(s, 1), kTall ? &p.tm_a : &p.tm_b, lead_bar, kb * S::kBK, r1,
+                                     kTall ? pol_a : pol_b);
+          ptx::tma_load_2d_pair_hint(smem_box(s, 2), &p.tm_b, lead_bar, kb * S::kBK, r2, pol_b);
         }
       }
     }
@@ -130,7 +139,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       bool alive = true;
       WorkItem w;
       auto issue_half = [&](int s, int h, bool first_kb) {
-        const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s));
+        const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s, h));
         const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s, h));
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(h) * S::kHalfN;
 #pragma unroll
@@ -187,11 +196,23 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
             break;
           }
           ptx::tc_fence_after();
-          issue_half(s, 0, false);
-          // Half 0 completes four UMMAs ahead of half 1: its epilogue starts (and hands the half back) while
-          // half 1 finishes, so the next tile's first UMMAs can queue up right behind this tile's last ones.
-          if (kb == num_kb - 1) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);
-          issue_half(s, 1, false);
+          if (kTall && kb != num_kb - 1) {
+            // both halves multiply by the same B: alternate so that neighbouring UMMAs share the operand
+            const uint64_t a0_desc = ptx::umma_desc_k_sw128(smem_a(s, 0));
+            const uint64_t a1_desc = ptx::umma_desc_k_sw128(smem_a(s, 1));
+            const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s, 0));
+#pragma unroll
+            for (int kk = 0; kk < S::kBK / 16; ++kk) {
+              ptx::umma_f16<2>(tmem_base, a0_desc + 2u * kk, b_desc + 2u * kk, idesc, 1u);
+              ptx::umma_f16<2>(tmem_base + S::kHalfN, a1_desc + 2u * kk, b_desc + 2u * kk, idesc, 1u);
+            }
+          } else {
+            issue_half(s, 0, false);
+            // Half 0 completes four UMMAs ahead of half 1: its epilogue starts (and hands the half back) while
+            // half 1 finishes, so the next tile's first UMMAs can queue up right behind this tile's last ones.
+            if (kb == num_kb - 1) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);
+            issue_half(s, 1, false);
+          }
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
         if (alive) ptx::umma_commit_pair_both(tmem_full_bar(1), 0x3);
@@ -204,8 +225,11 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     const uint32_t slot = warp - 2u;
     const uint32_t lead_empty0 = ptx::mapa(tmem_empty_bar(0), 0);
     const uint32_t lane_base = tmem_base + ((quad * 32u) << 16);
-    // chunk i of a tile: half (i >> 1), columns col_half * 128 + (i & 1) * 64 of that half
+    // chunk i of a tile: half (i >> 1), columns col_half * 128 + (i & 1) * 64 of that half's accumulator
     auto chunk_col = [&](int i) { return (i >> 1) * S::kHalfN + static_cast<int>(col_half) * 128 + (i & 1) * 64; };
+    // where chunk i lands in C relative to the tile's first row / column
+    auto out_row = [&](int i) { return kTall ? (i >> 1) * 256 : 0; };
+    auto out_col = [&](int i) { return kTall ? static_cast<int>(col_half) * 128 + (i & 1) * 64 : chunk_col(i); };
     uint32_t store_count = 0;
     WorkItem w;
     for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
@@ -218,8 +242,8 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       }
       BEAM_ACC_BEGIN();
       ptx::tc_fence_after();
-      const int row0 = w.mt * 256 + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
-      const int tile_col0 = w.nt * S::kTileN;
+      const int row0 = w.mt * (kTall ? 512 : 256) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
+      const int tile_col0 = w.nt * (kTall ? 256 : S::kTileN);
       // Both halves are handed back as soon as their accumulators sit in registers, before anything is rounded or
       // stored: the issuer's wait then depends on TMEM load latency only, not on how fast the (bursty, all CTAs at
       // once) C stores drain the staging buffers.
@@ -241,8 +265,9 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * h);
       };
       auto stage_and_store = [&](int i) {
-        const int col = tile_col0 + chunk_col(i);
-        if (col < p.n && row0 < p.m) {
+        const int col = tile_col0 + out_col(i);
+        const int row = row0 + out_row(i);
+        if (col < p.n && row < p.m) {
           constexpr uint32_t kBufs = S::kBufsPerWarp;
           const uint32_t buf = staging_base + (slot * kBufs + (store_count % kBufs)) * S::kStoreBufBytes;
           if (store_count >= kBufs) {
@@ -256,7 +281,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
                               out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) store_c_box(p, buf, col, row0);
+          if (lane == 0) store_c_box(p, buf, col, row);
           ++store_count;
         }
       };

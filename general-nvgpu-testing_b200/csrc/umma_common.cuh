@@ -22,14 +22,16 @@ enum DeviceFault : int {
 // abort flag, records `fault` in the global status word and returns false; callers then leave
 // their role loops and fall through to the common teardown, which still frees TMEM.
 constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
+constexpr uint32_t kSpinSuspendNs = 4000u;
 
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort,
                                              int* status_word, int fault) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0x3FFu) == 0) {
+    // suspended in hardware until the phase completes or kSpinSuspendNs pass: few instructions while waiting
+    if (ptx::mbar_try_wait_suspend(bar, parity, kSpinSuspendNs)) return true;
+    if ((spin & 0x3Fu) == 0) {
       if (*cta_abort) return false;
       const uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) {

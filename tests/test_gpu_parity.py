@@ -60,7 +60,7 @@ def test_config1_plumbing_512_cubed(beam, oracle_mod, name):
     assert oracle_mod.max_abs_over_max(c.cpu().numpy(), want) <= 2e-3
 
 
-@pytest.mark.parametrize("tb", [[128, 128], [128, 256], [256, 128], [256, 256], [256, 512]])
+@pytest.mark.parametrize("tb", [[128, 128], [128, 256], [256, 128], [256, 256], [256, 512], [512, 256]])
 def test_spec_tile_families(beam, oracle_mod, tb):
     a, b = _inputs(768, 512, 320, "uniform", 21)
     want = oracle_mod.gemmrc(a, b)
@@ -69,6 +69,20 @@ def test_spec_tile_families(beam, oracle_mod, tb):
     torch.cuda.synchronize()
     _healthy(beam)
     assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+
+
+def test_two_accumulator_tiles_without_persistence(beam):
+    """max_ctas = -1 launches one 256 x 512 (or 512 x 256) tile per CTA pair; the result is the persistent grid's, bit for bit."""
+    a, b = _inputs(1100, 1544, 712, 0.1, 4242)
+    da, db = _dev(a), _dev(b)
+    for kw in (dict(tile_n=512), dict(tile_n=256, tile_m=512)):
+        c0 = torch.zeros(1100, 1544, dtype=torch.float16, device="cuda")
+        c1 = torch.ones(1100, 1544, dtype=torch.float16, device="cuda")
+        beam.gemmrc(da, db, c0, cta_pair=2, **kw)
+        beam.gemmrc(da, db, c1, cta_pair=2, max_ctas=-1, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(c0, c1), kw
+    _healthy(beam)
 
 
 @pytest.mark.parametrize("case", ["tiny", "ragged", "tile", "wide", "deepk"])
@@ -86,7 +100,7 @@ def test_golden_vectors(beam, oracle_mod, case):
 
 @pytest.mark.parametrize("m,n,k", [(1, 8, 8), (8, 8, 8), (127, 136, 72), (129, 264, 200), (300, 1000, 1096),
                                     (257, 520, 64), (1000, 24, 4104)])
-@pytest.mark.parametrize("tile_n,cta_pair", [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2), (512, 2)])
+@pytest.mark.parametrize("tile_n,cta_pair", [(64, 1), (128, 1), (256, 1), (128, 2), (256, 2), (512, 2), (256, -2)])
 def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     """Edge tiles in M, N and K: out-of-range parts are zero-filled on load and masked on store, and nothing
     outside C[M,N] is written."""
@@ -94,7 +108,8 @@ def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     want = oracle_mod.gemmrc(a, b)
     guard = torch.full((m + 2, n), 3.0, dtype=torch.float16, device="cuda")
     c = guard[1:m + 1]
-    beam.gemmrc(_dev(a), _dev(b), c, tile_n=tile_n, cta_pair=cta_pair)
+    tile_m = 512 if cta_pair < 0 else 0  # cta_pair -2 stands for the 512 x 256 tile of a CTA pair
+    beam.gemmrc(_dev(a), _dev(b), c, tile_n=tile_n, cta_pair=abs(cta_pair), tile_m=tile_m)
     torch.cuda.synchronize()
     assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
     assert (guard[0] == 3.0).all() and (guard[m + 1] == 3.0).all()
