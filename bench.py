@@ -456,11 +456,13 @@ def run_profile_case(args):
     torch.cuda.set_device(0)
     torch.manual_seed(SEED)
     n_launch = max(args.steps, 1)
-    if args.profile in ("gemm", "cublas"):  # cublas: the comparison kernel on the same inputs
+    if args.profile in ("gemm", "gemm256", "cublas"):  # cublas: the comparison kernel on the same inputs
         a = (torch.randn(M_PER_GPU, K, device="cuda") * 0.1).half()
         b = (torch.randn(N, K, device="cuda") * 0.1).half()
         c = torch.zeros(M_PER_GPU, N, dtype=torch.float16, device="cuda")
-        fn = (lambda: beam.cublas_gemmexrc(a, b, c)) if args.profile == "cublas" else (lambda: beam.cutlass_gemmrc(a, b, c))
+        fn = {"cublas": lambda: beam.cublas_gemmexrc(a, b, c),
+              "gemm256": lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]),  # one accumulator per tile
+              "gemm": lambda: beam.cutlass_gemmrc(a, b, c)}[args.profile]
     elif args.profile in ("splitk", "splitk64"):
         m, n, k = (128, 256, 65536) if args.profile == "splitk" else (64, 64, 131072)
         a = (torch.rand(m, k, device="cuda") * 2 - 1).half()
@@ -491,7 +493,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the cuBLAS / split-K / LayerNorm side measurements")
-    ap.add_argument("--profile", default=None, choices=["gemm", "cublas", "splitk", "splitk64", "layernorm"],
+    ap.add_argument("--profile", default=None, choices=["gemm", "gemm256", "cublas", "splitk", "splitk64", "layernorm"],
                     help="run a few launches of one kernel and exit (the command the ncu captures in profiles/ wrap)")
     args = ap.parse_args()
     if args.profile:
