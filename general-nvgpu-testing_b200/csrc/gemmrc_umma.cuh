@@ -71,6 +71,7 @@ struct GemmParams {
   long long ew_count;
   int bf16;     // GEMM mode: A, B, C are bf16 instead of fp16 (same kernels: descriptor bits and final rounding)
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
+  int lead;     // two-accumulator tiles: k-blocks issued half-major at either end of a tile
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators

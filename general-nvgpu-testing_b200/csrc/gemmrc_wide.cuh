@@ -7,9 +7,10 @@
 // distinct operand rows per flop.
 //
 // The price: TMEM (512 columns) holds one tile, so the epilogue cannot hide behind the next tile's main loop
-// by double-buffering.  It hides behind the start of it instead: the first `kStages` k-blocks of a tile are
-// issued half-major (all of half 0, then all of half 1), so the issuer only needs half 0 drained to start
-// and half 1 is drained meanwhile.  The drain of half 0 is the exposed part, so the epilogue is made short:
+// by double-buffering.  It hides behind the ends of the main loops instead: the first and the last two
+// k-blocks of a tile are issued half-major (half 0 of both, then half 1 of both), so half 0 completes early
+// and is drained while half 1 finishes, and the issuer only needs half 0 back to start the next tile while
+// half 1 is drained.  The drain of half 0 is the exposed part, so the epilogue is made short:
 // eight warps (two per TMEM lane quadrant, 128 columns of each half apiece) pull a whole half into registers
 // and hand it back before rounding or storing anything, so the hand-back does not wait for the C stores.
 #pragma once
@@ -17,6 +18,19 @@
 #include "gemmrc_umma.cuh"
 
 namespace beam {
+
+#ifdef BEAM_TRACE
+// timeline of CTA 0 (diagnostic build): tagged time stamps appended to a region behind the per-CTA slots
+#define BEAM_TL(base, idx, tag)                                                                             \
+  do {                                                                                                      \
+    if (p.trace && blockIdx.x == 0 && (idx) < 1024u)                                                        \
+      p.trace[148 * 16 + (base) + (idx)++] = (static_cast<unsigned long long>(tag) << 56) | (ptx::globaltimer_ns() & 0xFFFFFFFFFFFFull); \
+  } while (0)
+#else
+#define BEAM_TL(base, idx, tag) \
+  do {                          \
+  } while (0)
+#endif
 
 template <int kStages>
 struct WideShape {
@@ -105,6 +119,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
+      [[maybe_unused]] uint32_t tl_p = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
@@ -122,6 +137,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
             alive = false;
             break;
           }
+          BEAM_TL(2048, tl_p, 21);
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
           const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
           ptx::tma_load_2d_pair_hint(smem_box(s, 0), &p.tm_a, lead_bar, kb * S::kBK, r0, pol_a);
@@ -136,6 +152,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kHalfN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       uint32_t it = 0;
+      [[maybe_unused]] uint32_t tl_m = 0;
       bool alive = true;
       WorkItem w;
       auto issue_half = [&](int s, int h, bool first_kb) {
@@ -146,39 +163,46 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         for (int kk = 0; kk < S::kBK / 16; ++kk)
           ptx::umma_f16<2>(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, (!first_kb || kk > 0) ? 1u : 0u);
       };
+      // A group of k-blocks issued half-major: half 0 of each (waiting for its bytes), then, after `between`,
+      // half 1 of each, which is also where their stages are released.
+      auto wait_landed = [&](uint32_t k) {
+        BEAM_ACC_BEGIN();
+        const bool landed = bounded_wait(full_bar(k % kStages), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
+        BEAM_ACC_END_T(14, 32);
+        if (landed) ptx::tc_fence_after();
+        return landed;
+      };
       for (int j = 0; alive && work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
         const uint32_t tile_ph = static_cast<uint32_t>(j) & 1u;
-        const int lead_in = num_kb < kStages ? num_kb : kStages;  // k-blocks issued half-major
-        // half 0 of the first k-blocks: needs only half 0 of the previous tile drained
+        // Tile boundary.  The first kLead k-blocks are issued half-major (needs only half 0 of the previous tile
+        // back; half 1 is being drained meanwhile) and so are the last kLead (half 0 completes early and is drained
+        // while half 1 finishes).  Longer groups pin more ring stages and starve the prefetch: two is the measured
+        // optimum for a 3- or 4-deep ring.
+        const int lead_in = num_kb < p.lead ? num_kb : p.lead;
+        const int lead_out = (num_kb - lead_in) < p.lead ? (num_kb - lead_in) : p.lead;
         {
           BEAM_ACC_BEGIN();
           const bool ok0 = bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
           BEAM_ACC_END_T(13, 32);
           if (!ok0) break;
         }
+        BEAM_TL(0, tl_m, 1);
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in && alive; ++g) {
-          const uint32_t k = it + static_cast<uint32_t>(g);
-          const int s = k % kStages;
-          BEAM_ACC_BEGIN();
-          const bool landed = bounded_wait(full_bar(s), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
-          BEAM_ACC_END_T(14, 32);
-          if (!landed) {
-            alive = false;
-            break;
-          }
-          ptx::tc_fence_after();
-          issue_half(s, 0, g == 0);
+          alive = wait_landed(it + static_cast<uint32_t>(g));
+          if (!alive) break;
+          BEAM_TL(0, tl_m, 2);
+          issue_half((it + static_cast<uint32_t>(g)) % kStages, 0, g == 0);
         }
         if (!alive) break;
         if (lead_in == num_kb) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);  // half 0 is complete already
-        // half 1 of the same k-blocks; their stages are released here
         {
           BEAM_ACC_BEGIN();
           const bool ok1 = bounded_wait(tmem_empty_bar(1), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
           BEAM_ACC_END_T(12, 32);
           if (!ok1) break;
         }
+        BEAM_TL(0, tl_m, 3);
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in; ++g) {
           const int s = (it + static_cast<uint32_t>(g)) % kStages;
@@ -186,17 +210,12 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
         it += static_cast<uint32_t>(lead_in);
-        for (int kb = lead_in; kb < num_kb; ++kb, ++it) {
+        for (int kb = lead_in; kb < num_kb - lead_out; ++kb, ++it) {
+          alive = wait_landed(it);
+          if (!alive) break;
           const int s = it % kStages;
-          BEAM_ACC_BEGIN();
-          const bool landed = bounded_wait(full_bar(s), (it / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
-          BEAM_ACC_END_T(14, 32);
-          if (!landed) {
-            alive = false;
-            break;
-          }
-          ptx::tc_fence_after();
-          if (kTall && kb != num_kb - 1) {
+          BEAM_TL(0, tl_m, 4);
+          if (kTall) {
             // both halves multiply by the same B: alternate so that neighbouring UMMAs share the operand
             const uint64_t a0_desc = ptx::umma_desc_k_sw128(smem_a(s, 0));
             const uint64_t a1_desc = ptx::umma_desc_k_sw128(smem_a(s, 1));
@@ -208,14 +227,29 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
             }
           } else {
             issue_half(s, 0, false);
-            // Half 0 completes four UMMAs ahead of half 1: its epilogue starts (and hands the half back) while
-            // half 1 finishes, so the next tile's first UMMAs can queue up right behind this tile's last ones.
-            if (kb == num_kb - 1) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);
             issue_half(s, 1, false);
           }
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
-        if (alive) ptx::umma_commit_pair_both(tmem_full_bar(1), 0x3);
+        if (!alive) break;
+        if (lead_out > 0) {
+          for (int g = 0; g < lead_out && alive; ++g) {
+            alive = wait_landed(it + static_cast<uint32_t>(g));
+            if (!alive) break;
+            BEAM_TL(0, tl_m, 6);
+            issue_half((it + static_cast<uint32_t>(g)) % kStages, 0, false);
+          }
+          if (!alive) break;
+          ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);  // half 0 is complete: its drain starts now
+          for (int g = 0; g < lead_out; ++g) {
+            const int s = (it + static_cast<uint32_t>(g)) % kStages;
+            issue_half(s, 1, false);
+            ptx::umma_commit_pair_both(empty_bar(s), 0x3);
+          }
+          it += static_cast<uint32_t>(lead_out);
+        }
+        ptx::umma_commit_pair_both(tmem_full_bar(1), 0x3);
+        BEAM_TL(0, tl_m, 5);
       }
     }
   } else {
@@ -231,6 +265,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     auto out_row = [&](int i) { return kTall ? (i >> 1) * 256 : 0; };
     auto out_col = [&](int i) { return kTall ? static_cast<int>(col_half) * 128 + (i & 1) * 64 : chunk_col(i); };
     uint32_t store_count = 0;
+    [[maybe_unused]] uint32_t tl_e = 0;
     WorkItem w;
     for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
       {
@@ -241,6 +276,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         if (!ready) break;
       }
       BEAM_ACC_BEGIN();
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 11);
       ptx::tc_fence_after();
       const int row0 = w.mt * (kTall ? 512 : 256) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
       const int tile_col0 = w.nt * (kTall ? 256 : S::kTileN);
@@ -289,10 +325,12 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       load_chunk(1, vb0, vb1);
       ptx::tmem_ld_wait();
       release_half(0);
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 12);
       round_chunk(va0, va1);
       if (!bounded_wait_warp(tmem_full_bar(1), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
                              kFaultEpilogueWait, lane))
         break;
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 13);
       ptx::tc_fence_after();
       load_chunk(2, va0, va1);
       stage_and_store(0);
@@ -300,11 +338,13 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       load_chunk(3, vb0, vb1);
       ptx::tmem_ld_wait();
       release_half(1);
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 14);
       stage_and_store(1);
       round_chunk(va0, va1);
       stage_and_store(2);
       round_chunk(vb0, vb1);
       stage_and_store(3);
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 15);
       BEAM_ACC_END(9);
     }
   }
