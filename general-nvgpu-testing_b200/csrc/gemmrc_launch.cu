@@ -201,7 +201,14 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.n_tiles = kTall ? (n + 255) / 256 : (n + S::kTileN - 1) / S::kTileN;
   p.group_m = group_m > 0 ? group_m : (kTall ? 8 : 16);
   p.slices = 1;
-  p.lead = 2;
+  p.lead_in = 2;
+  p.lead_out = 2;
+#ifdef BEAM_TRACE
+  if (g_debug_flags & 0xFF00) {
+    p.lead_in = (g_debug_flags >> 8) & 0xF;
+    p.lead_out = (g_debug_flags >> 12) & 0xF;
+  }
+#endif
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
   p.hint_c = (ex.l2_hints / 100) % 10;

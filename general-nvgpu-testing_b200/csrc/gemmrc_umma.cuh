@@ -71,7 +71,8 @@ struct GemmParams {
   long long ew_count;
   int bf16;     // GEMM mode: A, B, C are bf16 instead of fp16 (same kernels: descriptor bits and final rounding)
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
-  int lead;     // two-accumulator tiles: k-blocks issued half-major at either end of a tile
+  int lead_in;  // two-accumulator tiles: k-blocks issued half-major at the start of a tile (at least 1)
+  int lead_out; // ... and at its end
   int* status;  // device fault word
 #ifdef BEAM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators

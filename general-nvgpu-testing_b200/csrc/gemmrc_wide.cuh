@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         // back; half 1 is being drained meanwhile) and so are the last kLead (half 0 completes early and is drained
         // while half 1 finishes).  Longer groups pin more ring stages and starve the prefetch: two is the measured
         // optimum for a 3- or 4-deep ring.
-        const int lead_in = num_kb < p.lead ? num_kb : p.lead;
-        const int lead_out = (num_kb - lead_in) < p.lead ? (num_kb - lead_in) : p.lead;
+        const int lead_in = num_kb < p.lead_in ? num_kb : p.lead_in;
+        const int lead_out = (num_kb - lead_in) < p.lead_out ? (num_kb - lead_in) : p.lead_out;
         {
           BEAM_ACC_BEGIN();
           const bool ok0 = bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
@@ -232,6 +232,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }
         if (!alive) break;
+        if (lead_out == 0 && num_kb > lead_in) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);
         if (lead_out > 0) {
           for (int g = 0; g < lead_out && alive; ++g) {
             alive = wait_landed(it + static_cast<uint32_t>(g));
