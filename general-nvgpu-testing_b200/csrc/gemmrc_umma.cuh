@@ -686,11 +686,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
       constexpr bool kHalfOut = (kMode == kModeGemm || kMode == kModeGemmSilu);  // fp16 C through tm_c
       constexpr int kChunkCols = kHalfOut ? 64 : 32;
-#pragma unroll 1
       // Folded split-K: lanes 0..63 own the block in TMEM columns 0..63, lanes 64..127 the one in columns 64..127.
       const int fold_half = fold ? static_cast<int>(quad >> 1) : 0;
       const int c_begin = fold ? fold_half * 64 : 0;
       const int c_end = fold ? c_begin + 64 : BN;
+#pragma unroll 1
       for (int c = c_begin; c < c_end; c += kChunkCols) {
         uint32_t out[32];  // this row's 128 bytes of the chunk
         if constexpr (kHalfOut) {
