@@ -322,9 +322,12 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           ++store_count;
         }
       };
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 16);
       load_chunk(0, va0, va1);
       load_chunk(1, vb0, vb1);
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 17);
       ptx::tmem_ld_wait();
+      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 18);
       release_half(0);
       if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 12);
       round_chunk(va0, va1);
