@@ -1,8 +1,11 @@
 // Host launchers of the persistent UMMA kernels: validate the problem, pick the kernel
 // instantiation named by the plan, build the TMA descriptors and launch on the caller's stream.
+#include <cstdlib>
+
 #include "gemmrc_launch.h"
 
 #include "gemmrc_umma.cuh"
+#include "gemm_ln_resident.cuh"
 #include "gemmrc_wide.cuh"
 #include "layernorm_launch.h"
 #include "splitk_launch.h"
@@ -477,6 +480,67 @@ LnLayout ln_layout(int m, int n) {
 }
 }  // namespace
 
+// The TMEM-resident form (gemm_ln_resident.cuh): no parked panel, only statistics and tickets in the workspace.
+template <int kStages>
+int launch_ln_resident(DeviceCtx* ctx, const void* X, const void* W, void* out, const void* gamma, const void* beta,
+                       float eps, int m, int n, int k, float2* row_part, int* tickets, size_t ticket_bytes,
+                       cudaStream_t stream) {
+  using S = LnResidentShape<kStages>;
+  auto kernel = gemm_ln_resident_kernel<kStages>;
+  static bool configured[64] = {false};
+  if (!configured[ctx->device]) {
+    if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
+    BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
+                  "cudaFuncSetAttribute(smem)");
+    configured[ctx->device] = true;
+  }
+  GemmParams p = {};
+  int st = encode_tmap_2d(&p.tm_a, X, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                          static_cast<uint64_t>(k), S::kBM, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_b, W, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                      S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_c, out, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n),
+                      32, 64, true);
+  if (st != BEAM_OK) return st;
+  p.c = static_cast<__half*>(out);
+  p.row_part = row_part;
+  p.tickets = tickets;
+  p.gamma = static_cast<const __half*>(gamma);
+  p.beta = static_cast<const __half*>(beta);
+  p.eps = eps;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ldc = n;
+  p.m_tiles = (m + 255) / 256;
+  p.n_tiles = (n + S::kBN - 1) / S::kBN;
+  p.status = ctx->status_word;
+#ifdef BEAM_TRACE
+  p.trace = nullptr;
+  p.debug = 0;
+#endif
+  BEAM_CUDA_TRY(cudaMemsetAsync(tickets, 0, ticket_bytes, stream), "cudaMemsetAsync(tickets)");
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  int clusters = ctx->sm_count / 2;
+  if (tiles < clusters) clusters = static_cast<int>(tiles);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * 2), 1, 1);
+  cfg.blockDim = dim3(S::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemm_ln_resident)");
+  return BEAM_OK;
+}
+
 size_t layernorm_workspace_bytes(int m, int n, int k) {
   (void)k;
   if (m <= 0 || n <= 0) return 0;
@@ -506,9 +570,20 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   // Operand loads carry the explicit normal policy here: with the second pass's scratch traffic sharing L2,
   // this kernel measured 3 % slower when its operand reads were left eligible for request coalescing.
   ex.l2_hints = 33;
+  const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + kLnTileN - 1) / kLnTileN);
+  {
+    // With at least as many resident CTA pairs as N tiles (and enough tiles to occupy them), the tiles can wait
+    // in TMEM for their rows' statistics and nothing is parked: tickets (one int per 32 rows) go where the
+    // panel would have been.
+    const int pairs = ctx->sm_count / 2;
+    const int n_tiles_ = (n + kLnTileN - 1) / kLnTileN;
+    const size_t ticket_bytes = (static_cast<size_t>((m + 31) / 32) + 8) * sizeof(int);
+    if (pair_tiles >= pairs && n_tiles_ <= pairs && ticket_bytes <= l.panel_bytes && !getenv("BEAM_DEBUG_LN_PARKED"))
+      return launch_ln_resident<6>(ctx, X, W, out, gamma, beta, eps, m, n, k, ex.row_part,
+                                   reinterpret_cast<int*>(ws), ticket_bytes, stream);
+  }
   BEAM_CUDA_TRY(cudaMemsetAsync(ex.tickets, 0, l.ticket_bytes, stream), "cudaMemsetAsync(tickets)");
   // CTA pairs on 256-row tiles once there are enough tiles to fill the device; single CTAs otherwise.
-  const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + kLnTileN - 1) / kLnTileN);
   // Rasterisation: one wave of resident CTAs should cover whole rows of tiles, so that a panel's N tiles are
   // computed close together in time and its parked values are still in L2 when they are normalised.
   const int n_tiles = (n + kLnTileN - 1) / kLnTileN;
