@@ -273,7 +273,8 @@ def extras(beam, torch, a, b, c, peaks):
     out["gemm_layernorm_16384x4096x4096"] = {
         "ms": ms, "tflops": 2.0 * m * n * k / ms * 1e-9,
         "torch_matmul_plus_layer_norm_ms": ev_time(
-            lambda: torch.nn.functional.layer_norm(torch.matmul(x, w.t()), (n,), g, bt, 1e-5), 10)}
+            lambda: torch.nn.functional.layer_norm(torch.matmul(x, w.t()), (n,), g, bt, 1e-5), 10),
+        "gemm_alone_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(x, w, o, shape_threadblock=[256, 256]), 10)}
     return out
 
 

@@ -1,7 +1,5 @@
 // Host launchers of the persistent UMMA kernels: validate the problem, pick the kernel
 // instantiation named by the plan, build the TMA descriptors and launch on the caller's stream.
-#include <cstdlib>
-
 #include "gemmrc_launch.h"
 
 #include "gemmrc_umma.cuh"
@@ -578,7 +576,7 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
     const int pairs = ctx->sm_count / 2;
     const int n_tiles_ = (n + kLnTileN - 1) / kLnTileN;
     const size_t ticket_bytes = (static_cast<size_t>((m + 31) / 32) + 8) * sizeof(int);
-    if (pair_tiles >= pairs && n_tiles_ <= pairs && ticket_bytes <= l.panel_bytes && !getenv("BEAM_DEBUG_LN_PARKED"))
+    if (pair_tiles >= pairs && n_tiles_ <= pairs && ticket_bytes <= l.panel_bytes)
       return launch_ln_resident<6>(ctx, X, W, out, gamma, beta, eps, m, n, k, ex.row_part,
                                    reinterpret_cast<int*>(ws), ticket_bytes, stream);
   }

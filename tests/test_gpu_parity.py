@@ -271,6 +271,32 @@ def test_config4_layernorm_small(beam, oracle_mod, m, n, k):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("m,n,k,offset", [(2321, 2056, 200, 0.0), (4100, 1288, 72, 0.0), (2560, 2048, 512, 0.3),
+                                          (512, 19208, 64, 0.0)])
+def test_layernorm_tmem_resident_and_parked_paths(beam, oracle_mod, m, n, k, offset):
+    """Shapes with at least as many 256 x 256 tiles as CTA pairs and no more N tiles than pairs run the kernel that
+    keeps tiles in TMEM until their rows' statistics are complete (ragged M, N, K; a row mean several times the row's
+    spread -- much larger offsets make the fp32 accumulation order itself visible at this tolerance, for any
+    implementation); the last shape has more N tiles than pairs and takes the kernel that parks an fp32 panel."""
+    rng = np.random.Generator(np.random.PCG64(77 + m))
+    x = (rng.standard_normal((m, k)) * 0.05).astype(np.float16)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float16)
+    if offset:
+        x[:, 0] = np.float16(offset)
+        w[:, 0] = np.float16(1.0)       # every output gets +offset: mean = 5 x standard deviation
+    gamma = (1 + 0.1 * rng.standard_normal(n)).astype(np.float16)
+    beta = (0.1 * rng.standard_normal(n)).astype(np.float16)
+    want = oracle_mod.gemm_layernorm(x, w, gamma, beta, 1e-5)
+    out = torch.full((m, n), 9.0, dtype=torch.float16, device="cuda")
+    beam.cutlass_parallel_gemmrc_lnr(_dev(x), _dev(w), out, _dev(gamma), _dev(beta), 1e-5)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert oracle_mod.floored_max_rel(out.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    out2 = torch.zeros_like(out)
+    beam.cutlass_parallel_gemmrc_lnr(_dev(x), _dev(w), out2, _dev(gamma), _dev(beta), 1e-5)
+    assert torch.equal(out, out2)
+
+
 def test_golden_layernorm(beam, oracle_mod):
     g = np.load(GOLDEN)
     for case in ("ragged", "tile", "wide"):
