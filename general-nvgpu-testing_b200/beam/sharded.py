@@ -33,6 +33,16 @@ def sharded_gemmrc(a_local: torch.Tensor, b: torch.Tensor, c_local: torch.Tensor
     kernel(a_local, b, c_local)
 
 
+def sharded_gemm_layernorm(x_local: torch.Tensor, w: torch.Tensor, out_local: torch.Tensor, gamma: torch.Tensor,
+                           beta: torch.Tensor, eps: float = 1e-5) -> None:
+    """out_local = LayerNorm_row(x_local @ w.T) * gamma + beta on this rank's rows.  The statistics are per row, so
+    the row-sharded form needs no exchange either (BASELINE config 4 shards exactly like config 5)."""
+    if x_local.shape[0] == 0:
+        return
+    from . import _C
+    _C.cutlass_parallel_gemmrc_lnr(x_local, w, out_local, gamma, beta, eps)
+
+
 def all_gather_rows(c_local: torch.Tensor, m: int, group=None) -> torch.Tensor:
     """Assembles the full C [m, N] on every rank from the ranks' row blocks (row_block order).
     Equal blocks use one all_gather_into_tensor (a single NCCL all-gather over NVLink on GPUs);

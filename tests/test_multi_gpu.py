@@ -1,4 +1,4 @@
-"""Two-GPU test of the fused GEMM + all-gather (pytest -m gpu on a box with at least two GPUs; skipped otherwise).
+"""Two-GPU test of the fused GEMM + all-gather and of the row-sharded GEMM + LayerNorm (pytest -m gpu on a box with at least two GPUs; skipped otherwise).
 Each rank multiplies its row block and the kernel's epilogue stores every tile into both ranks' gathered buffers
 through peer-mapped (symmetric) memory; the result must equal the plain sharded GEMM followed by an NCCL all-gather."""
 import os
@@ -45,6 +45,23 @@ def _worker(rank, world, port, out_dir):
             got = gemmrc_allgather(a, b, gathered, **knobs)
             torch.cuda.synchronize()
             assert torch.equal(got, want), "rank %d shape %s" % (rank, (m_local, n, k))
+        # Row-sharded GEMM + LayerNorm: the statistics are per row, so the gathered result of the two ranks must be
+        # what one GPU computes for all rows.
+        from beam.sharded import sharded_gemm_layernorm
+        m_local, n, k = 2560, 2048, 256
+        xs = [(torch.randn(m_local, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(500 + r))
+               * 0.05).half() for r in range(world)]
+        gw = torch.Generator(device="cuda").manual_seed(9)
+        w = (torch.randn(n, k, device="cuda", generator=gw) * 0.05).half()
+        gamma = (1 + 0.1 * torch.randn(n, device="cuda", generator=gw)).half()
+        beta = (0.1 * torch.randn(n, device="cuda", generator=gw)).half()
+        out_local = torch.empty(m_local, n, dtype=torch.float16, device="cuda")
+        sharded_gemm_layernorm(xs[rank], w, out_local, gamma, beta, 1e-5)
+        got = all_gather_rows(out_local, m_local * world)
+        full = torch.empty(m_local * world, n, dtype=torch.float16, device="cuda")
+        beam.cutlass_parallel_gemmrc_lnr(torch.cat(xs), w, full, gamma, beta, 1e-5)
+        torch.cuda.synchronize()
+        assert torch.equal(got, full), "sharded LayerNorm, rank %d" % rank
         st, word = beam.device_status()
         assert (st, word) == (0, 0)
         open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
