@@ -463,11 +463,13 @@ constexpr int kLnTileN = 256;
 struct LnLayout {
   size_t panel_bytes, part_off, part_bytes, ticket_off, ticket_bytes, queue_off, total;  // ticket_bytes covers the queue too
 };
-LnLayout ln_layout(int m, int n) {
+// `resident`: the TMEM-resident kernel runs (it needs no panel; its tickets, one int per 32 rows, take the panel's place).
+LnLayout ln_layout(int m, int n, bool resident) {
   LnLayout l;
   const size_t n_tiles = static_cast<size_t>((n + kLnTileN - 1) / kLnTileN);
   const size_t panels = 2 * static_cast<size_t>((m + 255) / 256);  // both CTAs of every 256-row pair tile
-  l.panel_bytes = (static_cast<size_t>(m) * n * sizeof(float) + 255) / 256 * 256;
+  l.panel_bytes = resident ? ((static_cast<size_t>((m + 31) / 32) + 8) * sizeof(int) + 255) / 256 * 256
+                           : (static_cast<size_t>(m) * n * sizeof(float) + 255) / 256 * 256;
   l.part_off = l.panel_bytes;
   l.part_bytes = (static_cast<size_t>(m) * n_tiles * sizeof(float2) + 255) / 256 * 256;
   l.ticket_off = l.part_off + l.part_bytes;
@@ -476,6 +478,17 @@ LnLayout ln_layout(int m, int n) {
   l.total = l.ticket_off + l.ticket_bytes;
   return l;
 }
+// CTA pairs of the current device (74 when there is none to ask: sizes can be queried without a GPU).
+int ln_pairs() {
+  int sms = 148, dev = -1, err = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    if (DeviceCtx* ctx = current_device_ctx(&err)) sms = ctx->sm_count;
+  } else {
+    (void)cudaGetLastError();
+  }
+  return sms / 2;
+}
+bool ln_resident(int n) { return (n + kLnTileN - 1) / kLnTileN <= ln_pairs(); }
 }  // namespace
 
 // The TMEM-resident form (gemm_ln_resident.cuh): no parked panel, only statistics and tickets in the workspace.
@@ -542,7 +555,7 @@ int launch_ln_resident(DeviceCtx* ctx, const void* X, const void* W, void* out, 
 size_t layernorm_workspace_bytes(int m, int n, int k) {
   (void)k;
   if (m <= 0 || n <= 0) return 0;
-  return ln_layout(m, n).total;
+  return ln_layout(m, n, ln_resident(n)).total;
 }
 
 int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* gamma, const void* beta, float eps,
@@ -551,7 +564,8 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   if (st != BEAM_OK) return st;
   if (!gamma || !beta || !(eps >= 0.f)) return BEAM_ERR_INVALID_ARG;
   if (!aligned16(gamma) || !aligned16(beta)) return BEAM_ERR_ALIGNMENT;
-  const LnLayout l = ln_layout(m, n);
+  const bool resident = ln_resident(n);
+  const LnLayout l = ln_layout(m, n, resident);
   if (!workspace || workspace_bytes < l.total) return BEAM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return BEAM_ERR_ALIGNMENT;
   DeviceCtx* ctx = current_device_ctx(&st);
@@ -565,32 +579,25 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
   ex.gamma = static_cast<const __half*>(gamma);
   ex.beta = static_cast<const __half*>(beta);
   ex.eps = eps;
-  // Operand loads carry the explicit normal policy here: with the second pass's scratch traffic sharing L2,
-  // this kernel measured 3 % slower when its operand reads were left eligible for request coalescing.
-  ex.l2_hints = 33;
-  const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + kLnTileN - 1) / kLnTileN);
+  const int n_tiles = (n + kLnTileN - 1) / kLnTileN;
+  const int pairs = ctx->sm_count / 2;
   {
-    // With at least as many resident CTA pairs as N tiles (and enough tiles to occupy them), the tiles can wait
-    // in TMEM for their rows' statistics and nothing is parked: tickets (one int per 32 rows) go where the
-    // panel would have been.
-    const int pairs = ctx->sm_count / 2;
-    const int n_tiles_ = (n + kLnTileN - 1) / kLnTileN;
+    // With at least as many resident CTA pairs as N tiles, the tiles can wait in TMEM for their rows' statistics
+    // and nothing is parked: tickets (one int per 32 rows) go where the panel would have been.
     const size_t ticket_bytes = (static_cast<size_t>((m + 31) / 32) + 8) * sizeof(int);
-    if (pair_tiles >= pairs && n_tiles_ <= pairs && ticket_bytes <= l.panel_bytes)
+    if (resident && ticket_bytes <= l.panel_bytes)
       return launch_ln_resident<6>(ctx, X, W, out, gamma, beta, eps, m, n, k, ex.row_part,
                                    reinterpret_cast<int*>(ws), ticket_bytes, stream);
   }
+  // More N tiles than CTA pairs (N > 256 * pairs): the pre-normalisation values are parked as an fp32 panel.
+  // Operand loads carry the explicit normal policy here: with the second pass's scratch traffic sharing L2,
+  // that kernel measured 3 % slower when its operand reads were left eligible for request coalescing.
+  ex.l2_hints = 33;
   BEAM_CUDA_TRY(cudaMemsetAsync(ex.tickets, 0, l.ticket_bytes, stream), "cudaMemsetAsync(tickets)");
-  // CTA pairs on 256-row tiles once there are enough tiles to fill the device; single CTAs otherwise.
   // Rasterisation: one wave of resident CTAs should cover whole rows of tiles, so that a panel's N tiles are
   // computed close together in time and its parked values are still in L2 when they are normalised.
-  const int n_tiles = (n + kLnTileN - 1) / kLnTileN;
-  if (pair_tiles >= ctx->sm_count / 2) {
-    const int group_m = (ctx->sm_count / 2 + n_tiles - 1) / n_tiles;
-    return launch_instance<kLnTileN, 5, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, group_m, 0, ex, stream);
-  }
-  const int group_m = (ctx->sm_count + n_tiles - 1) / n_tiles;
-  return launch_instance<kLnTileN, 3, 1, kModeLayerNorm>(ctx, X, W, out, m, n, k, group_m, 0, ex, stream);
+  const int group_m = (pairs + n_tiles - 1) / n_tiles;
+  return launch_instance<kLnTileN, 5, 2, kModeLayerNorm>(ctx, X, W, out, m, n, k, group_m, 0, ex, stream);
 }
 
 }  // namespace beam

@@ -181,7 +181,9 @@ BEAM_API int beam_gemmrc_splitk_noalloc(const void* A, const void* B, void* C, i
 
 /* ---- fused GEMM + LayerNorm --------------------------------------------------------------------- */
 
-/* Scratch bytes for beam_gemmrc_layernorm: fp32 row statistics exchanged between the N-tiles. */
+/* Scratch bytes for beam_gemmrc_layernorm on the current device: row statistics exchanged between the N tiles
+ * (8 bytes per row per 256 columns) and tickets; when N needs more 256-wide tiles than the device has CTA pairs
+ * (N > 18944 on 148 SMs) also an fp32 panel of M x N. */
 BEAM_API size_t beam_gemmrc_layernorm_workspace_bytes(int m, int n, int k);
 
 /* Registry slot `cutlass_parallel_gemmrc_lnr` (cuda/cute_kernels/main.cc:55-76,87; the reference

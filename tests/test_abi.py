@@ -109,7 +109,11 @@ def test_splitk_sizing_functions(lib):
     ln = lib.beam_gemmrc_layernorm_workspace_bytes
     ln.restype = ctypes.c_size_t
     ln.argtypes = [i, i, i]
-    assert ln(16384, 4096, 4096) >= 16384 * 4096 * 4
+    # N tiles <= CTA pairs: tiles wait in TMEM, the workspace holds statistics (8 bytes per row per 256-wide tile)
+    # and tickets only; with more N tiles than pairs an fp32 panel is parked as well
+    assert 16384 * 16 * 8 <= ln(16384, 4096, 4096) < 16384 * 16 * 8 + (1 << 20)
+    assert ln(512, 256 * 80, 64) >= 512 * 256 * 80 * 4
+    assert ln(0, 64, 64) == 0
 
 
 def test_splitk_and_layernorm_reject_missing_workspace(lib):
