@@ -532,7 +532,13 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, BN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
-      uint32_t it = 0;
+      // The issuing thread is a single dependent instruction stream and, for N = 128, has only 256 clocks of tensor
+      // work per k-block to hide behind: the stage index and barrier parity advance incrementally (no division), the
+      // descriptors are the stage-0 descriptors plus a stride, and a k-block's four UMMAs are one instruction group.
+      uint32_t stage = 0, parity = 0;
+      const uint64_t a_desc0 = ptx::umma_desc_k_sw128(smem_a(0));
+      const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0));
+      constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
       bool alive = true;
       WorkItem w;
       for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
@@ -546,12 +552,10 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           {
             BEAM_ACC_BEGIN();
-            const bool landed = bounded_wait(full_bar(s), ph, cta_abort, p.status, kFaultMmaWaitFull);
+            const bool landed = bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull);
             BEAM_ACC_END_T(14, 32);
             if (!landed) {
               alive = false;
@@ -559,19 +563,17 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             }
           }
           ptx::tc_fence_after();
-          if (it == 0) BEAM_STAMP(3);
-          const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s));
-          const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s));
-#pragma unroll
-          for (int kk = 0; kk < S::kBK / 16; ++kk) {
-            // +32 bytes (2 x 16 B units) along K inside the 128-byte swizzle atom per UMMA.
-            ptx::umma_f16<kCta>(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc,
-                                (kb > w.kb0 || kk > 0) ? 1u : 0u);
-          }
+          if (j == 0 && kb == w.kb0) BEAM_STAMP(3);
+          ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride, idesc,
+                                     kb > w.kb0 ? 1u : 0u);
           if constexpr (kCta == 1)
-            ptx::umma_commit<1>(empty_bar(s));
+            ptx::umma_commit<1>(empty_bar(stage));
           else
-            ptx::umma_commit_pair_both(empty_bar(s), 0x3);
+            ptx::umma_commit_pair_both(empty_bar(stage), 0x3);
+          if (++stage == static_cast<uint32_t>(kStages)) {
+            stage = 0;
+            parity ^= 1u;
+          }
         }
         if (alive) {
           BEAM_STAMP(4);

@@ -285,6 +285,52 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                  : "memory");
 }
 // Pair form: the arrive lands on the mbarrier at this offset in every CTA named by cta_mask.
+// The four UMMAs (K = 16 each) of one 64-wide k-block as a single instruction group: descriptors advance by 32 bytes
+// (two 16-byte units) along K inside the 128-byte swizzle atom; only the first may start a fresh accumulator.
+template <int kCta>
+__device__ __forceinline__ void umma_f16_kblock(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+  if constexpr (kCta == 1)
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .b64 a, b;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "add.u64 a, %1, 2;\n\t"
+        "add.u64 b, %2, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 4;\n\t"
+        "add.u64 b, %2, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 6;\n\t"
+        "add.u64 b, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .b64 a, b;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "add.u64 a, %1, 2;\n\t"
+        "add.u64 b, %2, 2;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 4;\n\t"
+        "add.u64 b, %2, 4;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 6;\n\t"
+        "add.u64 b, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, q;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
