@@ -226,8 +226,15 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
               ptx::umma_f16<2>(tmem_base + S::kHalfN, a1_desc + 2u * kk, b_desc + 2u * kk, idesc, 1u);
             }
           } else {
-            issue_half(s, 0, false);
-            issue_half(s, 1, false);
+            // both halves multiply the same A: alternate, and let the second UMMA of each pair take A from the
+            // collector buffer the first one filled instead of reading shared memory again
+            const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s, 0));
+            const uint64_t b0_desc = ptx::umma_desc_k_sw128(smem_b(s, 0));
+            const uint64_t b1_desc = ptx::umma_desc_k_sw128(smem_b(s, 1));
+#pragma unroll
+            for (int kk = 0; kk < S::kBK / 16; ++kk)
+              ptx::umma_f16_pair_shared_a(tmem_base, tmem_base + S::kHalfN, a_desc + 2u * kk, b0_desc + 2u * kk,
+                                          b1_desc + 2u * kk, idesc, 1u, 1u);
           }
           ptx::umma_commit_pair_both(empty_bar(s), 0x3);
         }

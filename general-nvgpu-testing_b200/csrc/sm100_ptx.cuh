@@ -331,6 +331,22 @@ __device__ __forceinline__ void umma_f16_kblock(uint32_t d_tmem, uint64_t a_desc
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
+// Two UMMAs of a CTA pair that multiply the SAME A operand by two different B operands into two accumulators:
+// the first fills the A collector buffer, the second takes A from it instead of reading shared memory again.
+__device__ __forceinline__ void umma_f16_pair_shared_a(uint32_t d0_tmem, uint32_t d1_tmem, uint64_t a_desc,
+                                                       uint64_t b0_desc, uint64_t b1_desc, uint32_t idesc,
+                                                       uint32_t accumulate0, uint32_t accumulate1) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16.collector::a::fill [%0], %2, %3, %5, p;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16.collector::a::lastuse [%1], %2, %4, %5, q;\n\t"
+      "}\n" ::"r"(d0_tmem),
+      "r"(d1_tmem), "l"(a_desc), "l"(b0_desc), "l"(b1_desc), "r"(idesc), "r"(accumulate0), "r"(accumulate1)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
