@@ -145,9 +145,10 @@ _workspaces = {}
 
 
 def _workspace(device, nbytes):
-    """Grow-only scratch tensor per device, owned by the binding (the reference hides a cudaMalloc'd
-    buffer inside the extension instead: cutlass_gemmrc_splitk.cu:31-42)."""
-    key = (device.type, device.index)
+    """Grow-only scratch tensor per device and stream, owned by the binding (the reference hides a cudaMalloc'd
+    buffer inside the extension instead: cutlass_gemmrc_splitk.cu:31-42).  Per stream, because calls on different
+    streams may run at the same time and must not share partial sums or statistics."""
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)

@@ -158,6 +158,12 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;
   }
+  if (kMode == kModeLayerNorm) {
+    // CTAs of this grid wait for one another (the drain of the second pass): place the whole grid or none of it.
+    attr[1].id = cudaLaunchAttributeCooperative;
+    attr[1].val.cooperative = 1;
+    cfg.numAttrs = 2;
+  }
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
@@ -541,13 +547,17 @@ int launch_ln_resident(DeviceCtx* ctx, const void* X, const void* W, void* out, 
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // CTAs of this grid wait for one another: a cooperative launch places the whole grid or none of it, so two such
+  // grids launched on different streams cannot each hold half of the SMs and wait for the other half.
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemm_ln_resident)");
   return BEAM_OK;
 }

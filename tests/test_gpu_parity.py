@@ -297,6 +297,33 @@ def test_layernorm_tmem_resident_and_parked_paths(beam, oracle_mod, m, n, k, off
     assert torch.equal(out, out2)
 
 
+def test_layernorm_on_two_streams_at_once(beam):
+    """Two fused GEMM+LayerNorm grids in flight on different streams: the grids wait on their own CTAs, so each must be
+    placed as a whole (cooperative launch); results equal the one-stream results and no wait runs out."""
+    m, n, k = 4096, 2048, 1024
+    gen = torch.Generator(device="cuda").manual_seed(31)
+    xs = [(torch.randn(m, k, device="cuda", generator=gen) * 0.05).half() for _ in range(2)]
+    w = (torch.randn(n, k, device="cuda", generator=gen) * 0.05).half()
+    gamma = (1 + 0.1 * torch.randn(n, device="cuda", generator=gen)).half()
+    beta = (0.1 * torch.randn(n, device="cuda", generator=gen)).half()
+    want = []
+    for x in xs:
+        o = torch.empty(m, n, dtype=torch.float16, device="cuda")
+        beam.cutlass_parallel_gemmrc_lnr(x, w, o, gamma, beta, 1e-5)
+        want.append(o)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.zeros(m, n, dtype=torch.float16, device="cuda") for _ in range(2)]
+    for rep in range(10):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                beam.cutlass_parallel_gemmrc_lnr(xs[i], w, outs[i], gamma, beta, 1e-5)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    for i in range(2):
+        assert torch.equal(outs[i], want[i])
+
+
 def test_golden_layernorm(beam, oracle_mod):
     g = np.load(GOLDEN)
     for case in ("ragged", "tile", "wide"):
