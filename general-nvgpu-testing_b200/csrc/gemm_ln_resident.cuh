@@ -125,7 +125,10 @@ __global__ void __launch_bounds__(192, 1) gemm_ln_resident_kernel(const __grid_c
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
     if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kBN);
-      uint32_t it = 0;
+      uint32_t stage = 0, parity = 0;
+      const uint64_t a_desc0 = ptx::umma_desc_k_sw128(smem_a(0));
+      const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0));
+      constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
       bool alive = true;
       for (int j = 0; alive && j < my_tiles; ++j) {
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;
@@ -135,19 +138,19 @@ __global__ void __launch_bounds__(192, 1) gemm_ln_resident_kernel(const __grid_c
           break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * S::kBN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!bounded_wait(full_bar(s), (it / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull)) {
             alive = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint64_t a_desc = ptx::umma_desc_k_sw128(smem_a(s));
-          const uint64_t b_desc = ptx::umma_desc_k_sw128(smem_b(s));
-#pragma unroll
-          for (int kk = 0; kk < S::kBK / 16; ++kk)
-            ptx::umma_f16<2>(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-          ptx::umma_commit_pair_both(empty_bar(s), 0x3);
+          ptx::umma_f16_kblock<2>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride, idesc,
+                                  kb > 0 ? 1u : 0u);
+          ptx::umma_commit_pair_both(empty_bar(stage), 0x3);
+          if (++stage == static_cast<uint32_t>(kStages)) {
+            stage = 0;
+            parity ^= 1u;
+          }
         }
         if (alive) ptx::umma_commit_pair_both(tmem_full_bar(acc), 0x3);
       }
