@@ -7,7 +7,7 @@ built artefacts).  The reference's CMake build needs ccache and a populated CUTL
 exists here; this recipe compiles the same translation units directly against the CUTLASS/CuTe headers vendored
 in the image's site-packages, libtorch and pybind11.
 
-    python baseline/build_reference.py [/path/to/reference]
+    python baseline/build_reference.py /path/to/reference
 
 If a needed header tree is missing the script says so and exits 1; bench.py then reports the reference kernels
 as "not built".
@@ -24,7 +24,10 @@ OUT = os.path.join(HERE, "_ref")
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        print("usage: python baseline/build_reference.py /path/to/the/reference/checkout")
+        return 2
+    ref = sys.argv[1]
     cuda_dir = os.path.join(ref, "cuda")
     if not os.path.isdir(cuda_dir):
         print("reference checkout not found at", ref)

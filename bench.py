@@ -123,6 +123,31 @@ def cpu_sample(oracle, a_rows, b, seconds_target):
     return 2.0 * rows * b.shape[0] * b.shape[1] / dt * 1e-12, rows, dt
 
 
+def host_gemm_mkl(a_rows, b, seconds_target=4.0):
+    """The host GEMM a user of the reference would have at hand: torch-CPU fp32 `a.float() @ b.float().T` (MKL, all
+    threads) on the first rows of the workload, sized to a few seconds.  Returns a dict for the JSON line."""
+    import torch
+    try:
+        torch.set_num_threads(os.cpu_count() or 1)
+    except Exception:
+        pass
+    bf = torch.from_numpy(b).float()
+    probe = min(512, a_rows.shape[0])
+    af = torch.from_numpy(a_rows[:probe]).float()
+    torch.matmul(af, bf.t())  # first call: thread pool start-up
+    t0 = time.perf_counter()
+    torch.matmul(af, bf.t())
+    dt = max(time.perf_counter() - t0, 1e-4)
+    rows = int(min(a_rows.shape[0], max(probe, seconds_target / dt * probe)))
+    af = torch.from_numpy(a_rows[:rows]).float()
+    t0 = time.perf_counter()
+    torch.matmul(af, bf.t())
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows * b.shape[0] * b.shape[1] / dt * 1e-12, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "torch-CPU fp32 matmul (MKL), operands widened outside the timer",
+            "sample": "first %d rows of A x all of B (%d x %d x %d), %.2f s" % (rows, rows, b.shape[0], b.shape[1], dt)}
+
+
 def run_reference(args):
     """The reference has no CPU implementation of this path and its CUDA sources cannot be timed on host cores;
     its CPU-side statement (fp32 loop, oracle/gemmrc_oracle.c) is timed instead, all threads, bounded sample."""
@@ -153,40 +178,58 @@ def run_reference(args):
         "vs_baseline": None, "dtype": "f32 accumulate of f16 (CPU)", "data": "synthetic",
         "config": {"workload": "fp16 gemmrc 8192x8192x8192 (BASELINE configs[1]), sampled rows", "sample": sample},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-                         "sample": sample},
+                         "sample": sample, "host_gemm_mkl": host_gemm_mkl(a, b)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def reference_kernels(torch, a, b, c, ev_time):
-    """The reference's own kernels (its CuTe / CUTLASS sm80-era code, built unmodified for sm_100a by
-    baseline/build_reference.py) on the same inputs: comparison only."""
+def load_reference_module():
+    """The reference's own extension (its CuTe / CUTLASS sm80-era kernels, built unmodified for sm_100a by
+    baseline/build_reference.py into the git-ignored baseline/_ref): comparison only.  None if it is not built."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not any(f.startswith("beam_C") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
-        return "not built"
-    try:
+        return None
+    if ref_dir not in sys.path:
         sys.path.insert(0, ref_dir)
-        import beam_C  # prints its cuBLAS / CUTLASS versions to stderr
-        res = {}
-        want = torch.matmul(a, b.t()).float()
-        for name in ("custom_gemmrc_128x128", "custom_gemmrc_128x256", "cutlass_gemmrc"):
-            fn = getattr(beam_C, name)
+    import beam_C  # prints its cuBLAS / CUTLASS versions to stderr
+    return beam_C
+
+
+def reference_kernels(torch, beam_C, a, b, c, ev_time, do_bench_ms):
+    """The reference's large-GEMM kernels on the bench inputs: its two CuTe kernels, the CUTLASS default and the five
+    tile / warp instances of cutlass_gemmrc_spec (cuda/cutlass_kernels/cutlass_gemmrc.cu:105-110)."""
+    res = {}
+    want = torch.matmul(a, b.t()).float()
+    flop = 2.0 * M_PER_GPU * N * K
+    cases = [("custom_gemmrc_128x128", lambda: beam_C.custom_gemmrc_128x128(a, b, c)),
+             ("custom_gemmrc_128x256", lambda: beam_C.custom_gemmrc_128x256(a, b, c)),
+             ("cutlass_gemmrc", lambda: beam_C.cutlass_gemmrc(a, b, c))]
+    for tb, wp in (([128, 128], [64, 64]), ([128, 256], [64, 64]), ([256, 128], [64, 64]), ([256, 128], [128, 32]),
+                   ([256, 128], [32, 128])):
+        cases.append(("cutlass_gemmrc_spec_%dx%d_warp_%dx%d" % (tb[0], tb[1], wp[0], wp[1]),
+                      lambda tb=tb, wp=wp: beam_C.cutlass_gemmrc_spec(a, b, c, tb, wp)))
+    for name, fn in cases:
+        try:
             c.zero_()
-            ms = ev_time(lambda: fn(a, b, c), 5)
+            ms = ev_time(fn, 5)
             err = float((c.float() - want).abs().max() / want.abs().max())
-            res[name] = {"tflops": 2.0 * M_PER_GPU * N * K / ms * 1e-9, "max_abs_err_over_max": err}
-        return res
-    except Exception as ex:
-        return "failed: %r" % (ex,)
+            res[name] = {"tflops": flop / ms * 1e-9, "max_abs_err_over_max": err}
+            if name in ("custom_gemmrc_128x256", "cutlass_gemmrc"):
+                res[name]["do_bench_tflops"] = flop / do_bench_ms(fn) * 1e-9
+        except Exception as ex:
+            res[name] = "failed: %r" % (ex,)
+    return res
 
 
-def extras(beam, torch, a, b, c, peaks):
-    """Side measurements on rank 0 at N = 1 (bounded to a few seconds): cuBLAS on the same inputs, the split-K
-    shapes against the HBM roofline (CUDA-graph batches over rotating input sets larger than L2), and the fused
-    GEMM+LayerNorm."""
+def extras(beam, torch, a, b, c, peaks, clock_sampler):
+    """Side measurements on rank 0 at N = 1 (bounded to well under a minute of GPU time): cuBLAS on the same inputs,
+    every tile family, a sustained ours / cuBLAS comparison, the reference's own kernels, the split-K shapes against
+    the HBM roofline (CUDA-graph batches over rotating input sets larger than L2), GEMM + SiLU and GEMM + LayerNorm.
+    Every leg carries the SM clock and throttle reasons sampled while it ran."""
     out = {}
+    flop = 2.0 * M_PER_GPU * N * K
 
     def ev_time(fn, iters):
         for _ in range(3):
@@ -200,12 +243,89 @@ def extras(beam, torch, a, b, c, peaks):
         torch.cuda.synchronize()
         return s.elapsed_time(e) / iters
 
-    ms = ev_time(lambda: torch.matmul(a, b.t(), out=c), 20)
-    out["cublas_fp32acc_tflops"] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
-    for name, tb in (("128x128", [128, 128]), ("128x256", [128, 256]), ("256x128", [256, 128]),
-                     ("256x256", [256, 256]), ("256x512", [256, 512])):
-        ms = ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb), 10)
-        out["tile_%s_tflops" % name] = 2.0 * M_PER_GPU * N * K / ms * 1e-9
+    def do_bench_ms(fn):
+        """The reference's timer (python/gemm_test.py:73-75, python/beam/tuner.py:38-39): L2 flushed before every
+        repetition, 100 ms of warm-up, 100 ms of repetitions, mean."""
+        from triton.testing import do_bench
+        return float(do_bench(fn, warmup=100, rep=100))
+
+    def leg(name, fn):
+        """Runs one leg under its own clock sampler; a failing leg is reported, not raised."""
+        with clock_sampler() as clk:
+            try:
+                res = fn()
+            except Exception as ex:
+                res = {"error": repr(ex)}
+        if isinstance(res, dict):
+            res["clocks"] = clk.summary()
+        out[name] = res
+
+    beam_C = None
+    try:
+        beam_C = load_reference_module()
+    except Exception as ex:
+        out["reference_module_error"] = repr(ex)
+
+    def large_gemm_leg():
+        r = {"cublas_fp32acc_tflops": flop / ev_time(lambda: torch.matmul(a, b.t(), out=c), 20) * 1e-9}
+        for name, tb in (("128x128", [128, 128]), ("128x256", [128, 256]), ("256x128", [256, 128]),
+                         ("256x256", [256, 256]), ("256x512", [256, 512])):
+            ms = ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=tb), 10)
+            r["tile_%s_tflops" % name] = flop / ms * 1e-9
+        return r
+
+    leg("large_gemm_8192", large_gemm_leg)
+    # kept at the top level too: earlier records read these keys there
+    if "error" not in out["large_gemm_8192"]:
+        for k_, v_ in out["large_gemm_8192"].items():
+            if k_ != "clocks":
+                out[k_] = v_
+
+    def do_bench_leg():
+        r = {"timer": "triton.testing.do_bench(warmup=100, rep=100), the reference's timer: L2 flushed before each call"}
+        r["ours_cutlass_gemmrc_tflops"] = flop / do_bench_ms(lambda: beam.cutlass_gemmrc(a, b, c)) * 1e-9
+        r["cublas_tflops"] = flop / do_bench_ms(lambda: torch.matmul(a, b.t(), out=c)) * 1e-9
+        return r
+
+    leg("do_bench_8192", do_bench_leg)
+
+    def sustained_leg():
+        """Ours and cuBLAS in alternating blocks (A B A B), about 2 s of launches each after a common warm-up, so that
+        both see the same power-capped clock regime; reported as TFLOP/s and as SM cycles per launch (time x median
+        SM clock of that arm's own samples), which separates the kernel from the clock it was given."""
+        ours = lambda: beam.cutlass_gemmrc(a, b, c)
+        cub = lambda: torch.matmul(a, b.t(), out=c)
+        for _ in range(300):
+            ours()
+        torch.cuda.synchronize()
+        per_block, blocks = 700, 4
+        arms = {"ours": {"ms": 0.0, "mhz": []}, "cublas": {"ms": 0.0, "mhz": []}}
+        for blk in range(2 * blocks):
+            name, fn = ("ours", ours) if blk % 2 == 0 else ("cublas", cub)
+            with clock_sampler() as clk:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(per_block):
+                    fn()
+                e.record()
+                torch.cuda.synchronize()
+            arms[name]["ms"] += s.elapsed_time(e)
+            arms[name]["mhz"] += clk.samples
+        r = {"launches_per_arm": per_block * blocks, "pattern": "ABAB blocks of %d launches after 300 warm-up launches" % per_block}
+        for name, d in arms.items():
+            ms = d["ms"] / (per_block * blocks)
+            mhz = sorted(d["mhz"])[len(d["mhz"]) // 2] if d["mhz"] else None
+            r[name] = {"tflops": flop / ms * 1e-9, "ms_per_launch": ms, "seconds": d["ms"] * 1e-3, "sm_mhz_median": mhz,
+                       "sm_cycles_per_launch": ms * 1e-3 * mhz * 1e6 if mhz else None}
+        r["ours_over_cublas"] = r["ours"]["tflops"] / r["cublas"]["tflops"]
+        return r
+
+    leg("sustained_8192_ours_vs_cublas", sustained_leg)
+
+    if beam_C is not None:
+        leg("reference_kernels_sm80_on_b200", lambda: reference_kernels(torch, beam_C, a, b, c, ev_time, do_bench_ms))
+    else:
+        out["reference_kernels_sm80_on_b200"] = "not built"
 
     def graph_us(fns):
         for f in fns:
@@ -230,7 +350,7 @@ def extras(beam, torch, a, b, c, peaks):
             ts.append(s.elapsed_time(e) / len(fns) * 1e3)
         return sorted(ts)[len(ts) // 2]
 
-    for (m, n, k) in ((128, 256, 65536), (64, 64, 131072)):
+    def splitk_leg(m, n, k):
         # A ~10 us kernel timed straight after a power-saturating GEMM loop measures the throttled clock the
         # GEMMs left behind (both this kernel and cuBLAS read 40 % slower for about a second), so let it settle.
         torch.cuda.synchronize()
@@ -240,41 +360,77 @@ def extras(beam, torch, a, b, c, peaks):
         Bs = [(torch.rand(n, k, device="cuda") * 2 - 1).half() for _ in range(sets)]
         cc = torch.zeros(m, n, dtype=torch.float16, device="cuda")
         bytes_ = 2.0 * (m * k + n * k + m * n)
-        # "overlapped": BEAM_FLAG_INPUTS_STABLE, i.e. consecutive calls may stream side by side (the inputs of a
-        # call are never the outputs of the call before it here); "plain": every call waits for the one before.
-        us_plain = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc))
-                             for i in range(24)])
-        us = graph_us([(lambda i=i: beam.cutlass_gemmrc_splitk(As[i % sets], Bs[i % sets], cc, inputs_stable=True))
-                       for i in range(24)])
-        gbs = bytes_ / (us * 1e-6) * 1e-9
-        out["splitk_%dx%dx%d" % (m, n, k)] = {
-            "us_overlapped": us, "us_plain": us_plain, "algorithmic_bytes": bytes_, "GBps": gbs,
-            "hbm_peak_GBps": peaks["hbm_gbs"], "frac_of_%s_hbm" % peaks["source"]: gbs / peaks["hbm_gbs"],
-            "frac_plain": bytes_ / (us_plain * 1e-6) * 1e-9 / peaks["hbm_gbs"],
-            "cublas_us": graph_us([(lambda i=i: torch.matmul(As[i % sets], Bs[i % sets].t(), out=cc))
-                                   for i in range(24)])}
-        del As, Bs
-    # GEMM with a co-scheduled element-wise SiLU over a second tensor (what the reference's cute_gemm_ln.cu does)
-    xs = torch.randn(64 << 20, device="cuda", dtype=torch.float16)
-    ys = torch.empty_like(xs)
-    out["gemm_8192_plus_silu_64Mi"] = {
-        "fused_ms": ev_time(lambda: beam.cutlass_parallel_gemmrc_silu(a, b, c, xs, ys), 10),
-        "gemm_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]), 10),
-        "torch_silu_ms": ev_time(lambda: torch.nn.functional.silu(xs, inplace=False), 10)}
-    del xs, ys
-    out["reference_kernels_sm80_on_b200"] = reference_kernels(torch, a, b, c, ev_time)
-    m, n, k = 16384, 4096, 4096
-    x = (torch.randn(m, k, device="cuda") * 0.02).half()
-    w = (torch.randn(n, k, device="cuda") * 0.02).half()
-    g = (1 + 0.1 * torch.randn(n, device="cuda")).half()
-    bt = (0.1 * torch.randn(n, device="cuda")).half()
-    o = torch.empty(m, n, dtype=torch.float16, device="cuda")
-    ms = ev_time(lambda: beam.cutlass_parallel_gemmrc_lnr(x, w, o, g, bt, 1e-5), 10)
-    out["gemm_layernorm_16384x4096x4096"] = {
-        "ms": ms, "tflops": 2.0 * m * n * k / ms * 1e-9,
-        "torch_matmul_plus_layer_norm_ms": ev_time(
-            lambda: torch.nn.functional.layer_norm(torch.matmul(x, w.t()), (n,), g, bt, 1e-5), 10),
-        "gemm_alone_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(x, w, o, shape_threadblock=[256, 256]), 10)}
+        roof = lambda us: bytes_ / (us * 1e-6) * 1e-9 / peaks["hbm_gbs"]
+        batch = lambda fn: graph_us([(lambda i=i: fn(As[i % sets], Bs[i % sets])) for i in range(24)])
+        # "plain": every call waits for the call before it (a chain of dependent calls, no promise from the caller);
+        # "overlapped": BEAM_FLAG_INPUTS_STABLE, consecutive calls may stream side by side.
+        r = {"algorithmic_bytes": bytes_, "hbm_peak_GBps": peaks["hbm_gbs"], "peak_source": peaks["source"],
+             "plan_plain": beam.splitk_describe(m, n, k), "plan_overlapped": beam.splitk_describe(m, n, k, inputs_stable=True)}
+        r["us_plain"] = batch(lambda x, y: beam.cutlass_gemmrc_splitk(x, y, cc))
+        r["us_plain_two_kernels"] = batch(lambda x, y: beam.cutlass_gemmrc_splitk(x, y, cc, two_kernels=True))
+        r["us_overlapped"] = batch(lambda x, y: beam.cutlass_gemmrc_splitk(x, y, cc, inputs_stable=True))
+        r["us_overlapped_two_kernels"] = batch(lambda x, y: beam.cutlass_gemmrc_splitk(x, y, cc, inputs_stable=True,
+                                                                                        two_kernels=True))
+        r["frac_plain"] = roof(r["us_plain"])
+        r["frac_plain_two_kernels"] = roof(r["us_plain_two_kernels"])
+        us = min(r["us_overlapped"], r["us_overlapped_two_kernels"])
+        r["GBps"] = bytes_ / (us * 1e-6) * 1e-9
+        r["frac_of_%s_hbm" % peaks["source"]] = roof(us)
+        r["cublas_us"] = batch(lambda x, y: torch.matmul(x, y.t(), out=cc))
+        if beam_C is not None:
+            # the reference's own split-K (CUTLASS GemmSplitKParallel + ReduceSplitK, two launches on the legacy
+            # stream, its own slice heuristic); its default instance and the 64 x 64 one, the only one sized for M = N = 64
+            want = torch.matmul(As[0], Bs[0].t()).float()
+            for name, fn in (("reference_cutlass_gemmrc_splitk_us", lambda x, y: beam_C.cutlass_gemmrc_splitk(x, y, cc, 0)),
+                             ("reference_splitk_spec_64x64_us",
+                              lambda x, y: beam_C.cutlass_gemmrc_splitk_spec(x, y, cc, [64, 64], [32, 32], 0))):
+                try:
+                    cc.zero_()
+                    fn(As[0], Bs[0])
+                    torch.cuda.synchronize()
+                    err = float((cc.float() - want).abs().max() / want.abs().max())
+                    if err > 1e-2:
+                        r[name] = "did not compute this shape (max abs err / max = %.3g)" % err
+                        continue
+                    s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    s_.record(torch.cuda.default_stream())
+                    for i in range(24):
+                        fn(As[i % sets], Bs[i % sets])
+                    e_.record(torch.cuda.default_stream())
+                    torch.cuda.synchronize()
+                    r[name] = s_.elapsed_time(e_) / 24 * 1e3
+                except Exception as ex:
+                    r[name] = "failed: %r" % (ex,)
+        return r
+
+    for (m, n, k) in ((128, 256, 65536), (64, 64, 131072)):
+        leg("splitk_%dx%dx%d" % (m, n, k), lambda: splitk_leg(m, n, k))
+
+    def silu_leg():
+        # GEMM with a co-scheduled element-wise SiLU over a second tensor (what the reference's cute_gemm_ln.cu does)
+        xs = torch.randn(64 << 20, device="cuda", dtype=torch.float16)
+        ys = torch.empty_like(xs)
+        return {"fused_ms": ev_time(lambda: beam.cutlass_parallel_gemmrc_silu(a, b, c, xs, ys), 10),
+                "gemm_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]), 10),
+                "torch_silu_ms": ev_time(lambda: torch.nn.functional.silu(xs, inplace=False), 10)}
+
+    leg("gemm_8192_plus_silu_64Mi", silu_leg)
+
+    def layernorm_leg():
+        m, n, k = 16384, 4096, 4096
+        x = (torch.randn(m, k, device="cuda") * 0.02).half()
+        w = (torch.randn(n, k, device="cuda") * 0.02).half()
+        g = (1 + 0.1 * torch.randn(n, device="cuda")).half()
+        bt = (0.1 * torch.randn(n, device="cuda")).half()
+        o = torch.empty(m, n, dtype=torch.float16, device="cuda")
+        ms = ev_time(lambda: beam.cutlass_parallel_gemmrc_lnr(x, w, o, g, bt, 1e-5), 10)
+        return {"ms": ms, "tflops": 2.0 * m * n * k / ms * 1e-9,
+                "torch_matmul_plus_layer_norm_ms": ev_time(
+                    lambda: torch.nn.functional.layer_norm(torch.matmul(x, w.t()), (n,), g, bt, 1e-5), 10),
+                "gemm_alone_ms": ev_time(lambda: beam.cutlass_gemmrc_spec(x, w, o, shape_threadblock=[256, 256]), 10)}
+
+    leg("gemm_layernorm_16384x4096x4096", layernorm_leg)
     return out
 
 
@@ -377,7 +533,6 @@ def run_ours(args):
         gather = {"nccl_all_gather_ms": gather_ms, "bytes_received_per_gpu": recv_bytes,
                   "GBps_in_per_gpu": recv_bytes / (gather_ms * 1e-3) * 1e-9,
                   "tflops_gemm_then_nccl_gather": flops_step_all / ((ms_step + gather_ms) * 1e-3) * 1e-12}
-        del full
         # The same result from ONE kernel per rank: the GEMM epilogue stores each tile into every rank's gathered
         # buffer (peer-mapped symmetric memory) while the main loop runs on.
         try:
@@ -399,9 +554,16 @@ def run_ours(args):
             mine = gc.tensor[rank * M_PER_GPU:(rank + 1) * M_PER_GPU]
             gather["fused_gemm_gather_ms"] = fused_ms
             gather["tflops_fused"] = flops_step_all / (fused_ms * 1e-3) * 1e-12
+            gather["GBps_in_per_gpu_fused"] = recv_bytes / (fused_ms * 1e-3) * 1e-9
             gather["fused_matches"] = bool(torch.equal(mine, c))
+            # Every block of this rank's gathered buffer (its own and the world - 1 blocks that the peers' kernels
+            # stored over NVLink) against the NCCL all-gather of the same C blocks, on every rank.
+            all_ok = torch.tensor([1 if torch.equal(gc.tensor, full) else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(all_ok, op=dist.ReduceOp.MIN)
+            gather["fused_matches_all_blocks"] = bool(int(all_ok.item()) == 1)
         except Exception as ex:
             gather["fused_error"] = repr(ex)
+        del full
 
     if rank == 0:
         burst = ms_total < 500.0  # a short run sits in the burst regime, a long one under the power cap
@@ -438,10 +600,12 @@ def run_ours(args):
             tf, rows, dt = cpu_sample(oracle, ha.numpy(), hb.numpy(), 10.0)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                                     "sample": "first %d rows of A x all of B (%d x %d x %d), %.1f s" %
-                                              (rows, rows, N, K, dt)}
+                                              (rows, rows, N, K, dt),
+                                    "host_gemm_mkl": host_gemm_mkl(ha.numpy(), hb.numpy())}
             if not args.no_extras:
                 try:
-                    line["extras"] = extras(beam, torch, a, b, c, peaks)
+                    line["extras"] = extras(beam, torch, a, b, c, peaks,
+                                            lambda: ClockSampler(physical_index(local)))
                 except Exception as ex:  # side measurements never take the headline down
                     line["extras"] = {"error": repr(ex)}
         print(json.dumps(line), flush=True)

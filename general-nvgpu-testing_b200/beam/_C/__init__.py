@@ -30,6 +30,8 @@ __all__ = [
     "gemmrc",
     "gemmrc_host",
     "gemmrc_allgather",
+    "splitk_describe",
+    "release_workspaces",
     "BeamError",
     "library_path",
 ]
@@ -87,6 +89,7 @@ def _load():
     L.beam_gemmrc_splitk_workspace_bytes.restype = sz
     L.beam_gemmrc_splitk_workspace_bytes.argtypes = [i, i, i, i, i]
     L.beam_gemmrc_splitk_heuristic.argtypes = [i, i, i, i]
+    L.beam_gemmrc_splitk_describe.argtypes = [i, i, i, i, i, i, ctypes.POINTER(i)]
     L.beam_cutlass_gemmrc_splitk.argtypes = [vp, vp, vp, i, i, i, i, vp, sz, vp]
     L.beam_gemmrc_splitk_fp16.argtypes = [vp, vp, vp, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp, sz, vp]
     L.beam_cutlass_gemmrc_splitk_spec.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, vp, sz, vp]
@@ -156,6 +159,12 @@ def _workspace(device, nbytes):
     return ws
 
 
+def release_workspaces():
+    """Drops the scratch tensors the binding keeps per device and stream (they are grow-only otherwise).  The
+    caller makes sure that no split-K or LayerNorm call is still running."""
+    _workspaces.clear()
+
+
 def _run(fn_name, a, b, c, *extra):
     m, n, k = _check_abc(a, b, c)
     L = _load()
@@ -213,12 +222,27 @@ def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hi
 
 
 FLAG_INPUTS_STABLE = 1
+FLAG_SPLITK_TWO_KERNELS = 4
 
 
-def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable):
+def splitk_describe(m, n, k, tile_n=0, split_k_slices=0, inputs_stable=False, two_kernels=False):
+    """How a split-K call with these arguments runs on the current device: a dict with the tile N, the number of K
+    slices, whether the problem runs folded, the kernels per call (1 or 2) and whether the first kernel is a
+    programmatic dependent launch."""
+    info = (ctypes.c_int * 5)()
+    flags = (FLAG_INPUTS_STABLE if inputs_stable else 0) | (FLAG_SPLITK_TWO_KERNELS if two_kernels else 0)
+    st = _load().beam_gemmrc_splitk_describe(int(m), int(n), int(k), int(tile_n), int(split_k_slices), flags, info)
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_splitk_describe")
+    return {"tile_n": info[0], "slices": info[1], "folded": bool(info[2]), "kernels_per_call": info[3],
+            "programmatic_dependent_launch": bool(info[4])}
+
+
+def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable, two_kernels=False):
     m, n, k = _check_abc(a, b, c)
     L = _load()
-    cfg = beam_gemm_cfg(int(tile_n), 0, 0, 0, int(split_k_slices), 0, 0, FLAG_INPUTS_STABLE if inputs_stable else 0)
+    flags = (FLAG_INPUTS_STABLE if inputs_stable else 0) | (FLAG_SPLITK_TWO_KERNELS if two_kernels else 0)
+    cfg = beam_gemm_cfg(int(tile_n), 0, 0, 0, int(split_k_slices), 0, 0, flags)
     with torch.cuda.device(a.device):
         nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, int(tile_n), int(split_k_slices))
         if nbytes > (4 << 30):
@@ -230,23 +254,24 @@ def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable):
         _raise(st, "beam_gemmrc_splitk_fp16")
 
 
-def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0, inputs_stable=False):
+def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0, inputs_stable=False, two_kernels=False):
     """Split-K c = a @ b.T for small M, N and huge K; fp32 partials summed in a fixed order (bitwise
     reproducible).  split_k_slices = 0 lets the library choose (slot of cutlass_gemmrc_splitk.cu:59-105).
     inputs_stable=True promises that a and b are not outputs of the kernel just before this call on the
-    stream, which lets back-to-back calls overlap (BEAM_FLAG_INPUTS_STABLE)."""
-    _splitk(a, b, c, 0, split_k_slices, inputs_stable)
+    stream, which lets back-to-back calls overlap (BEAM_FLAG_INPUTS_STABLE).  two_kernels=True forces the
+    partials-then-reduction pair of kernels where the library would run the call as one kernel (same bits)."""
+    _splitk(a, b, c, 0, split_k_slices, inputs_stable, two_kernels)
 
 
 def cutlass_gemmrc_splitk_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64], split_k_slices=0,
-                               inputs_stable=False):
+                               inputs_stable=False, two_kernels=False):
     """Split-K with the tile's N taken from shape_threadblock[1] (64, 128 or 256); shape_warp is accepted for
     signature compatibility (cuda/cutlass_kernels/main.cc:137-141) and ignored."""
     tbm, tbn = _pair(shape_threadblock, "shape_threadblock")
     _pair(shape_warp, "shape_warp")
     if tbn not in (64, 128, 256):
         raise ValueError("shape_threadblock[1] must be 64, 128 or 256")
-    _splitk(a, b, c, tbn, split_k_slices, inputs_stable)
+    _splitk(a, b, c, tbn, split_k_slices, inputs_stable, two_kernels)
 
 
 def cutlass_parallel_gemmrc_lnr(a, b, c, gamma, beta, eps=1e-5):
@@ -343,7 +368,18 @@ def cublas_gemmexrc(a, b, c):
 
 
 def cublas_hgemmrc(a, b, c):
-    """cuBLAS Hgemm slot (reference: cuda/cublas.cc:44-71).  torch exposes one fp16 matmul; whether it
-    accumulates in fp16 is governed by torch.backends.cuda.matmul.allow_fp16_accumulation."""
+    """cuBLAS Hgemm slot (reference: cuda/cublas.cc:44-71, fp16 compute type).  Comparison baseline: torch's
+    fp16 matmul with fp16 accumulation switched on for the duration of the call
+    (torch.backends.cuda.matmul.allow_fp16_accumulation), which is what selects cuBLAS's fp16-compute kernels.
+    On a torch build without that switch this is the same call as cublas_gemmexrc."""
     _check_abc(a, b, c)
-    torch.matmul(a, b.t(), out=c)
+    mm = torch.backends.cuda.matmul
+    if not hasattr(mm, "allow_fp16_accumulation"):
+        torch.matmul(a, b.t(), out=c)
+        return
+    saved = mm.allow_fp16_accumulation
+    mm.allow_fp16_accumulation = True
+    try:
+        torch.matmul(a, b.t(), out=c)
+    finally:
+        mm.allow_fp16_accumulation = saved

@@ -64,6 +64,27 @@ def do_bench(fn: Callable[[], None], warmup_ms: float = 25.0, rep_ms: float = 10
     return times[len(times) // 2]
 
 
+SPLITK_SCRATCH_LIMIT = 256 << 20  # bytes of fp32 partials (slices * M * N * 4) a split-K candidate may ask for
+
+
+def _is_splitk(op) -> bool:
+    f = op.func.func if isinstance(op.func, partial) else op.func
+    return "splitk" in getattr(f, "__name__", "")
+
+
+def _splitk_can_pay_off(op, m: int, n: int, sms: int) -> bool:
+    """Split-K exists for problems whose output tiles cannot fill the device.  Once the 128 x 128 tiles of C alone
+    occupy every SM, slicing K only adds a round trip of fp32 partials, and with an explicit split factor the
+    scratch (slices * M * N * 4 bytes, kept by the binding for the life of the process) can reach gigabytes:
+    such candidates are not timed."""
+    tiles = -(-m // 128) * -(-n // 128)
+    if tiles >= sms:
+        return False
+    kw = op.func.keywords if isinstance(op.func, partial) else {}
+    slices = int(kw.get("split_k_slices", 0)) or max(1, sms // tiles)
+    return slices * m * n * 4 <= SPLITK_SCRATCH_LIMIT
+
+
 class Operator:
     def __init__(self, func: Callable):
         self.func = func
@@ -195,8 +216,10 @@ class OperatorTuner:
         a = torch.randn(M, K, dtype=torch.float16, device="cuda")
         b = torch.randn(N, K, dtype=torch.float16, device="cuda")
         c = torch.randn(M, N, dtype=torch.float16, device="cuda")
+        sms = torch.cuda.get_device_properties(a.device).multi_processor_count
         for op in self.gemm_ops:
-            # Split-K of a large-MN problem needs slices * M * N * 4 bytes of scratch: skip what cannot pay off.
+            if _is_splitk(op) and not _splitk_can_pay_off(op, M, N, sms):
+                continue
             tflops = op.get_performance(a, b, c)
             if tflops > best_tflops:
                 best_op = op

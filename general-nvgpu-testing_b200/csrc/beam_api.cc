@@ -129,6 +129,10 @@ size_t beam_gemmrc_splitk_workspace_bytes(int m, int n, int k, int tile_n, int s
 
 int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n) { return splitk_heuristic(m, n, k, tile_n); }
 
+int beam_gemmrc_splitk_describe(int m, int n, int k, int tile_n, int split_k_slices, int flags, int* info) {
+  return splitk_describe(m, n, k, tile_n, split_k_slices, flags, info);
+}
+
 int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n, int k, const beam_gemm_cfg* cfg,
                             void* workspace, size_t workspace_bytes, void* stream) {
   int tile_n = 0, slices = 0, flags = 0;
@@ -137,7 +141,7 @@ int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n,
     slices = cfg->split_k_slices;
     flags = cfg->flags;
     if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return BEAM_ERR_UNSUPPORTED;
-    if (flags & ~BEAM_FLAG_INPUTS_STABLE) return BEAM_ERR_INVALID_ARG;
+    if (flags & ~(BEAM_FLAG_INPUTS_STABLE | BEAM_FLAG_SPLITK_TWO_KERNELS)) return BEAM_ERR_INVALID_ARG;
   }
   return launch_splitk(A, B, C, m, n, k, tile_n, slices, workspace, workspace_bytes,
                        static_cast<cudaStream_t>(stream), flags);

@@ -2,6 +2,8 @@
 // instantiation named by the plan, build the TMA descriptors and launch on the caller's stream.
 #include "gemmrc_launch.h"
 
+#include <mutex>
+
 #include "gemmrc_umma.cuh"
 #include "gemm_ln_resident.cuh"
 #include "gemmrc_wide.cuh"
@@ -10,15 +12,6 @@
 
 namespace beam {
 
-#ifdef BEAM_TRACE
-// Diagnostic builds only (never part of the shipped library): where kernels drop their time stamps.
-static unsigned long long* g_trace_buffer = nullptr;
-static int g_debug_flags = 0;
-extern "C" __attribute__((visibility("default"))) void beam_debug_set_flags(int flags) { g_debug_flags = flags; }
-extern "C" __attribute__((visibility("default"))) void beam_debug_set_trace(unsigned long long* device_buffer) {
-  g_trace_buffer = device_buffer;
-}
-#endif
 
 namespace {
 
@@ -42,6 +35,29 @@ struct ExtraArgs {
   int* ln_queue = nullptr;
 };
 
+// How many 2-CTA clusters of `kernel` the device holds at once (a GPC with an odd number of free SMs leaves one
+// unpaired, so this can be less than half the SM count).
+template <typename Kernel>
+int resident_pairs(Kernel kernel, int threads, int smem_bytes, int sm_count) {
+  int pairs = sm_count / 2;
+  cudaLaunchConfig_t probe = {};
+  probe.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2), 1, 1);
+  probe.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  probe.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  probe.attrs = attr;
+  probe.numAttrs = 1;
+  int n_clusters = 0;
+  cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, kernel, &probe);
+  if (e == cudaSuccess && n_clusters > 0 && n_clusters < pairs) pairs = n_clusters;
+  (void)cudaGetLastError();
+  return pairs > 0 ? pairs : 1;
+}
+
 template <int BN, int kStages, int kCta, int kMode>
 int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
                     int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
@@ -51,34 +67,25 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   // One-time per (instantiation, device): opt in to the large dynamic shared memory and, for
   // pairs, ask how many 2-CTA clusters fit on this part at once.
   static int configured_clusters[64] = {0};
-  int& resident = configured_clusters[ctx->device];
+  static std::mutex configure_mutex;
+  int resident = 0;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    resident = configured_clusters[ctx->device];
+  }
   if (resident == 0) {
+    std::lock_guard<std::mutex> lock(configure_mutex);
     if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
     BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
                   "cudaFuncSetAttribute(smem)");
     int clusters = ctx->sm_count / kCta;
-    if (kCta == 2) {
-      cudaLaunchConfig_t probe = {};
-      probe.gridDim = dim3(static_cast<unsigned>(ctx->sm_count / 2 * 2), 1, 1);
-      probe.blockDim = dim3(S::kThreads, 1, 1);
-      probe.dynamicSmemBytes = S::kSmemBytes;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      probe.attrs = attr;
-      probe.numAttrs = 1;
-      int n_clusters = 0;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, kernel, &probe);
-      if (e == cudaSuccess && n_clusters > 0 && n_clusters < clusters) clusters = n_clusters;
-      (void)cudaGetLastError();
-    }
+    if (kCta == 2) clusters = resident_pairs(kernel, S::kThreads, S::kSmemBytes, ctx->sm_count);
     resident = clusters > 0 ? clusters : 1;
+    configured_clusters[ctx->device] = resident;
   }
 
   GemmParams p = {};
-  const bool fold = kMode == kModeSplitK && BN == 128 && kCta == 1 && ex.fold != 0;
+  const bool fold = is_splitk_mode(kMode) && BN == 128 && kCta == 1 && ex.fold != 0;
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(k), fold ? S::kBM / 2 : S::kBM, S::kBK, true);
   if (st != BEAM_OK) return st;
@@ -129,42 +136,52 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.hint_c = (ex.l2_hints / 100) % 10;
   p.flags = ex.flags;
   p.status = ctx->status_word;
-#ifdef BEAM_TRACE
-  p.trace = g_trace_buffer;
-  p.debug = g_debug_flags;
-#endif
 
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
   if (items < clusters) clusters = static_cast<int>(items);
+  // One kernel per split-K call: every CTA takes exactly one (tile, slice) and all of them meet at a grid-wide
+  // barrier, so the grid must fit on the device at once.  The caller checks that before choosing this mode.
+  if (kMode == kModeSplitKFused && items > clusters) return BEAM_ERR_UNSUPPORTED;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCta), 1, 1);
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kCta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (kMode == kModeSplitK) {
+  if (kMode == kModeLayerNorm || kMode == kModeSplitKFused) {
+    // CTAs of this grid wait for one another (the drain of LayerNorm's second pass; the barrier in front of the
+    // split-K sum): place the whole grid or none of it.
+    attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
+    attr[cfg.numAttrs].val.cooperative = 1;
+    ++cfg.numAttrs;
+  }
+  if (is_splitk_mode(kMode) && !(kMode == kModeSplitKFused && ctx->coop_without_pdl)) {
     // May start while the previous kernel on the stream drains; the kernel itself waits for that grid's
     // completion before its first global read or write.
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.numAttrs = 2;
+    attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++cfg.numAttrs;
   }
-  if (kMode == kModeLayerNorm) {
-    // CTAs of this grid wait for one another (the drain of the second pass): place the whole grid or none of it.
-    attr[1].id = cudaLaunchAttributeCooperative;
-    attr[1].val.cooperative = 1;
-    cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
+  if (kMode == kModeSplitKFused && e != cudaSuccess && !ctx->coop_without_pdl &&
+      (e == cudaErrorNotSupported || e == cudaErrorInvalidValue || e == cudaErrorInvalidConfiguration)) {
+    // This driver does not take a cooperative grid as a programmatic dependent: launch it as an ordinary
+    // stream-ordered kernel from now on (griddepcontrol.wait then returns at once).
+    (void)cudaGetLastError();
+    ctx->coop_without_pdl = true;
+    --cfg.numAttrs;
+    e = cudaLaunchKernelEx(&cfg, kernel, p);
   }
-  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
+  BEAM_CUDA_TRY(e, "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
 
@@ -175,12 +192,19 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   using S = WideShape<kStages>;
   auto kernel = gemmrc_wide_kernel<kStages, kTall>;
   static int configured_clusters[64] = {0};
-  int& resident = configured_clusters[ctx->device];
+  static std::mutex configure_mutex;
+  int resident = 0;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    resident = configured_clusters[ctx->device];
+  }
   if (resident == 0) {
+    std::lock_guard<std::mutex> lock(configure_mutex);
     if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
     BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
                   "cudaFuncSetAttribute(smem)");
-    resident = ctx->sm_count / 2 > 0 ? ctx->sm_count / 2 : 1;
+    resident = resident_pairs(kernel, S::kThreads, S::kSmemBytes, ctx->sm_count);
+    configured_clusters[ctx->device] = resident;
   }
   GemmParams p = {};
   int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
@@ -210,20 +234,10 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.slices = 1;
   p.lead_in = 2;
   p.lead_out = 2;
-#ifdef BEAM_TRACE
-  if (g_debug_flags & 0xFF00) {
-    p.lead_in = (g_debug_flags >> 8) & 0xF;
-    p.lead_out = (g_debug_flags >> 12) & 0xF;
-  }
-#endif
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
   p.hint_c = (ex.l2_hints / 100) % 10;
   p.status = ctx->status_word;
-#ifdef BEAM_TRACE
-  p.trace = g_trace_buffer;
-  p.debug = 0;
-#endif
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles;
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
@@ -414,6 +428,32 @@ size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
   return planes * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
 }
 
+// The one-kernel form needs every (tile, slice) resident at once (one CTA per SM) and a device that launches
+// cooperative grids; BEAM_FLAG_SPLITK_TWO_KERNELS asks for the two-kernel form regardless.
+static bool splitk_one_kernel(const DeviceCtx* ctx, int m, int n, int bn, int slices, int flags) {
+  if (flags & BEAM_FLAG_SPLITK_TWO_KERNELS) return false;
+  if (!ctx->cooperative_launch) return false;
+  const long long items = static_cast<long long>((m + 127) / 128) * ((n + bn - 1) / bn) * slices;
+  return items <= ctx->sm_count;
+}
+
+int splitk_describe(int m, int n, int k, int tile_n, int slices, int flags, int* info) {
+  int st = BEAM_OK;
+  DeviceCtx* ctx = current_device_ctx(&st);
+  if (!ctx) return st;
+  if (m <= 0 || n <= 0 || k <= 0 || slices < 0 || !info) return BEAM_ERR_INVALID_ARG;
+  const bool fold = splitk_folds(m, n, tile_n);
+  const int bn = fold ? 128 : splitk_tile_n(n, tile_n);
+  const int s = splitk_resolve_slices(m, n, k, tile_n, slices, flags);
+  const bool one = splitk_one_kernel(ctx, m, n, bn, s, flags);
+  info[0] = bn;
+  info[1] = s;
+  info[2] = fold ? 1 : 0;
+  info[3] = one ? 1 : 2;                                 // kernels per call
+  info[4] = (one && ctx->coop_without_pdl) ? 0 : 1;      // first kernel is a programmatic dependent launch
+  return BEAM_OK;
+}
+
 int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, int tile_n, int slices,
                   void* workspace, size_t workspace_bytes, cudaStream_t stream, int flags) {
   int st = validate_gemm_args(A, B, C, m, n, k);
@@ -433,8 +473,15 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   ExtraArgs ex;
   ex.scratch = static_cast<float*>(workspace);
   ex.slices = s;
-  ex.flags = flags;
+  ex.flags = flags & BEAM_FLAG_INPUTS_STABLE;
   ex.fold = fold ? 1 : 0;
+  if (splitk_one_kernel(ctx, m, n, bn, s, flags)) {
+    // One kernel: partials, a grid-wide barrier, then every CTA sums its share of the output (same order as the
+    // reduction kernel below, so the two paths agree bit for bit).
+    if (bn == 64) return launch_instance<64, 8, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    if (bn == 128) return launch_instance<128, 6, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    return launch_instance<256, 4, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+  }
   if (bn == 64)
     st = launch_instance<64, 8, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
   else if (bn == 128)
@@ -484,15 +531,34 @@ LnLayout ln_layout(int m, int n, bool resident) {
   l.total = l.ticket_off + l.ticket_bytes;
   return l;
 }
+constexpr int kLnResidentStages = 6;
+// CTA pairs of the TMEM-resident kernel that the device holds at once, asked of the occupancy calculator once per
+// device (which also opts the kernel in to its shared memory); 0 if the kernel cannot run there.
+int ln_resident_pairs(DeviceCtx* ctx) {
+  using S = LnResidentShape<kLnResidentStages>;
+  static int cached[64] = {0};
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  int& pairs = cached[ctx->device];
+  if (pairs == 0) {
+    pairs = -1;
+    if (S::kSmemBytes <= ctx->max_smem_optin &&
+        cudaFuncSetAttribute(gemm_ln_resident_kernel<kLnResidentStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             S::kSmemBytes) == cudaSuccess)
+      pairs = resident_pairs(gemm_ln_resident_kernel<kLnResidentStages>, S::kThreads, S::kSmemBytes, ctx->sm_count);
+    (void)cudaGetLastError();
+  }
+  return pairs > 0 ? pairs : 0;
+}
 // CTA pairs of the current device (74 when there is none to ask: sizes can be queried without a GPU).
 int ln_pairs() {
-  int sms = 148, dev = -1, err = 0;
+  int dev = -1, err = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) {
-    if (DeviceCtx* ctx = current_device_ctx(&err)) sms = ctx->sm_count;
+    if (DeviceCtx* ctx = current_device_ctx(&err)) return ln_resident_pairs(ctx);
   } else {
     (void)cudaGetLastError();
   }
-  return sms / 2;
+  return 74;
 }
 bool ln_resident(int n) { return (n + kLnTileN - 1) / kLnTileN <= ln_pairs(); }
 }  // namespace
@@ -504,13 +570,8 @@ int launch_ln_resident(DeviceCtx* ctx, const void* X, const void* W, void* out, 
                        cudaStream_t stream) {
   using S = LnResidentShape<kStages>;
   auto kernel = gemm_ln_resident_kernel<kStages>;
-  static bool configured[64] = {false};
-  if (!configured[ctx->device]) {
-    if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
-    BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
-                  "cudaFuncSetAttribute(smem)");
-    configured[ctx->device] = true;
-  }
+  const int pairs = ln_resident_pairs(ctx);  // also opts the kernel in to its shared memory, once per device
+  if (pairs <= 0) return BEAM_ERR_UNSUPPORTED;
   GemmParams p = {};
   int st = encode_tmap_2d(&p.tm_a, X, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(k), S::kBM, S::kBK, true);
@@ -534,13 +595,9 @@ int launch_ln_resident(DeviceCtx* ctx, const void* X, const void* W, void* out, 
   p.m_tiles = (m + 255) / 256;
   p.n_tiles = (n + S::kBN - 1) / S::kBN;
   p.status = ctx->status_word;
-#ifdef BEAM_TRACE
-  p.trace = nullptr;
-  p.debug = 0;
-#endif
   BEAM_CUDA_TRY(cudaMemsetAsync(tickets, 0, ticket_bytes, stream), "cudaMemsetAsync(tickets)");
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-  int clusters = ctx->sm_count / 2;
+  int clusters = pairs;
   if (tiles < clusters) clusters = static_cast<int>(tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * 2), 1, 1);
@@ -596,7 +653,7 @@ int launch_gemm_layernorm(const void* X, const void* W, void* out, const void* g
     // and nothing is parked: tickets (one int per 32 rows) go where the panel would have been.
     const size_t ticket_bytes = (static_cast<size_t>((m + 31) / 32) + 8) * sizeof(int);
     if (resident && ticket_bytes <= l.panel_bytes)
-      return launch_ln_resident<6>(ctx, X, W, out, gamma, beta, eps, m, n, k, ex.row_part,
+      return launch_ln_resident<kLnResidentStages>(ctx, X, W, out, gamma, beta, eps, m, n, k, ex.row_part,
                                    reinterpret_cast<int*>(ws), ticket_bytes, stream);
   }
   // More N tiles than CTA pairs (N > 256 * pairs): the pre-normalisation values are parked as an fp32 panel.

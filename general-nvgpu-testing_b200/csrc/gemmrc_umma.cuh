@@ -23,6 +23,9 @@
 //   kModeGemm       fp32 -> fp16, store C.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
+//   kModeSplitKFused  the same partials, but the grid is launched cooperatively with exactly one work item per
+//                   CTA; after a grid-wide barrier every CTA sums the slices of its share of the output in the
+//                   same fixed order and stores fp16: one kernel per call, no second launch to wait for.
 //   kModeGemmSilu   the GEMM epilogue, plus an unrelated element-wise y = x / (1 + exp(-x)) over a second tensor
 //                   that the epilogue warps work through, 1024 elements at a time, while they wait for their
 //                   next accumulator (what the reference's cute_gemm_ln.cu co-schedules on a quarter of its CTAs).
@@ -35,11 +38,14 @@
 //                   second pass is spread over all SMs and hidden under the main loops.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "umma_common.cuh"
 
 namespace beam {
 
-enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3 };
+enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3, kModeSplitKFused = 4 };
+__host__ __device__ constexpr bool is_splitk_mode(int mode) { return mode == kModeSplitK || mode == kModeSplitKFused; }
 
 struct GemmParams {
   CUtensorMap tm_a;  // A  [M, K], box 128 x 64, 128 B swizzle
@@ -74,37 +80,7 @@ struct GemmParams {
   int lead_in;  // two-accumulator tiles: k-blocks issued half-major at the start of a tile (at least 1)
   int lead_out; // ... and at its end
   int* status;  // device fault word
-#ifdef BEAM_TRACE
-  unsigned long long* trace;  // diagnostic builds only: 16 words per CTA, 8 stamps + 8 accumulators
-  int debug;                  // diagnostic builds only: 1 = skip the output stores, 2 = every tile loads tile (0,0)
-#endif
 };
-
-#ifdef BEAM_TRACE
-#define BEAM_STAMP(slot)                                                                      \
-  do {                                                                                        \
-    if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * 16 + (slot)] = ptx::globaltimer_ns(); \
-  } while (0)
-#define BEAM_ACC_BEGIN() const unsigned long long beam_acc_t0 = ptx::globaltimer_ns()
-#define BEAM_ACC_END_T(slot, tid)                                                                                \
-  do {                                                                                                         \
-    if (p.trace && threadIdx.x == (tid)) p.trace[static_cast<size_t>(blockIdx.x) * 16 + (slot)] += ptx::globaltimer_ns() - beam_acc_t0; \
-  } while (0)
-#define BEAM_ACC_END(slot) BEAM_ACC_END_T(slot, 64)
-#else
-#define BEAM_STAMP(slot) \
-  do {                   \
-  } while (0)
-#define BEAM_ACC_BEGIN() \
-  do {                   \
-  } while (0)
-#define BEAM_ACC_END(slot) \
-  do {                     \
-  } while (0)
-#define BEAM_ACC_END_T(slot, tid) \
-  do {                            \
-  } while (0)
-#endif
 
 template <int BN, int kStages, int kCta, int kMode = kModeGemm>
 struct GemmShape {
@@ -154,7 +130,7 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk,
   w.slice = 0;
   w.kb0 = 0;
   w.kb1 = num_kb;
-  if constexpr (kMode != kModeSplitK) {
+  if constexpr (!is_splitk_mode(kMode)) {
     const int t = first + j * stride;
     if (t >= p.m_tiles * p.n_tiles) return false;
     const int per_group = p.group_m * p.n_tiles;
@@ -376,6 +352,82 @@ __device__ __forceinline__ int ln_visit(const GemmParams& p, int& pending, uint3
   return done != 0 ? kLnAllDone : kLnIdle;
 }
 
+// ------------------------------------------------------------------ split-K: fixed-order sum of the partials
+// C[r][c] = fp16( sum over planes of partial[plane][r][c] ), the planes dealt to kReduceGroups groups of
+// consecutive planes: inside a group the planes are added in ascending order, then the group sums are added
+// in ascending group order.  The association depends only on the plane count, never on timing or on how the
+// work is spread over threads, so results are bitwise reproducible, and the two callers below (the reduction
+// kernel of the two-kernel path and the tail of the one-kernel path) produce identical bits.
+constexpr int kReduceGroups = 8;
+constexpr int kReduceUnitsPerPass = 16;  // float4 output groups that 128 threads (8 groups x 16) reduce together
+
+// Threads 0..127 of the CTA reduce output units [u0, u1) (a unit = 4 consecutive columns of one row; units are
+// numbered row-major).  kUnroll units per thread and kBatch planes per unit are loaded before anything is
+// added, so kUnroll * kBatch 16-byte loads are in flight per thread.  `sums` is shared memory for
+// kReduceGroups x kReduceUnitsPerPass x kUnroll float4.  Called by every thread of the CTA (uniform trip count).
+template <int kUnroll, int kBatch>
+__device__ __forceinline__ void splitk_reduce_share(const float* __restrict__ partial, __half* __restrict__ c, int m,
+                                                    int n, int planes, long long u0, long long u1, float4* sums) {
+  const int t = static_cast<int>(threadIdx.x);
+  const int g = t >> 4;        // plane group of this thread (only t < 128 work)
+  const int q = t & 15;
+  const int n4 = n >> 2;
+  const size_t plane_stride = static_cast<size_t>(m) * n;
+  const int s0 = planes * g / kReduceGroups;
+  const int s1 = planes * (g + 1) / kReduceGroups;
+  for (long long base = u0; base < u1; base += kReduceUnitsPerPass * kUnroll) {
+    if (t < 128) {
+      float4 acc[kUnroll];
+      const float* src[kUnroll];
+      bool live[kUnroll];
+#pragma unroll
+      for (int i = 0; i < kUnroll; ++i) {
+        const long long u = base + q + i * kReduceUnitsPerPass;
+        live[i] = u < u1;
+        const long long uu = live[i] ? u : u0;
+        src[i] = partial + (uu / n4) * n + (uu % n4) * 4;
+        acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      for (int s = s0; s < s1; s += kBatch) {
+        float4 v[kUnroll][kBatch];
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i)
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b)
+            v[i][b] = (live[i] && s + b < s1) ? __ldcg(reinterpret_cast<const float4*>(src[i] + plane_stride * (s + b)))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i)
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b)
+            if (s + b < s1) {
+              acc[i].x += v[i][b].x; acc[i].y += v[i][b].y; acc[i].z += v[i][b].z; acc[i].w += v[i][b].w;
+            }
+      }
+#pragma unroll
+      for (int i = 0; i < kUnroll; ++i) sums[(g * kUnroll + i) * kReduceUnitsPerPass + q] = acc[i];
+    }
+    __syncthreads();
+    if (t < kReduceUnitsPerPass * kUnroll) {
+      const int i = t >> 4;
+      const long long u = base + q + i * kReduceUnitsPerPass;
+      if (u < u1) {
+        float4 r = sums[i * kReduceUnitsPerPass + q];
+#pragma unroll
+        for (int gg = 1; gg < kReduceGroups; ++gg) {
+          const float4 w = sums[(gg * kUnroll + i) * kReduceUnitsPerPass + q];
+          r.x += w.x; r.y += w.y; r.z += w.z; r.w += w.w;
+        }
+        uint2 o;
+        o.x = ptx::pack_half2(r.x, r.y);
+        o.y = ptx::pack_half2(r.z, r.w);
+        *reinterpret_cast<uint2*>(c + (u / n4) * n + (u % n4) * 4) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 template <int BN, int kStages, int kCta, int kMode>
 __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmShape<BN, kStages, kCta, kMode>;
@@ -383,15 +435,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) BEAM_STAMP(0);
-#ifdef BEAM_TRACE
-  if (threadIdx.x == 0 && p.trace) {
-    uint32_t smid, nsmid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    asm volatile("mov.u32 %0, %%nsmid;" : "=r"(nsmid));
-    p.trace[static_cast<size_t>(blockIdx.x) * 16 + 15] = (static_cast<unsigned long long>(nsmid) << 32) | smid;
-  }
-#endif
   const uint32_t cta_rank = (kCta == 2) ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
   Walk walk;
@@ -419,7 +462,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   // N = 128 UMMA computes [A_2i; A_2i+1] x [B_2i; B_2i+1]^T, whose two diagonal 64 x 64 blocks are the wanted
   // products (the off-diagonal blocks are ignored).  No shared-memory row is zero fill, and the ring holds twice
   // as much of K.  The two diagonal blocks leave as two partial slices (2 * slice, 2 * slice + 1).
-  constexpr bool kCanFold = (kMode == kModeSplitK) && BN == 128 && kCta == 1;
+  constexpr bool kCanFold = is_splitk_mode(kMode) && BN == 128 && kCta == 1;
   const bool fold = kCanFold && p.fold != 0;
   const int num_kb = fold ? ((p.k + S::kBK - 1) / S::kBK + 1) / 2 : (p.k + S::kBK - 1) / S::kBK;
   auto load_stage = [&](int s, int kb, int row_a, int row_b, uint64_t pol_a_, uint64_t pol_b_) {  // one CTA per tile
@@ -452,13 +495,14 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
-    if constexpr (kMode == kModeSplitK) {
+    if constexpr (is_splitk_mode(kMode)) {
       // Launched as a programmatic dependent of the previous call's reduction: everything above may run
       // while that grid drains; nothing below reads or writes global memory before it has completed.
       // With BEAM_FLAG_INPUTS_STABLE the caller vouches that A and B are not that grid's outputs, and the
       // loads below may start at once; the partial stores wait for it in the epilogue either way.
       if (!(p.flags & 1)) ptx::grid_dependency_wait();
-      // In turn, let this call's reduction kernel become resident early; it blocks until this grid is done.
+      // In turn, let the next kernel on the stream (this call's reduction kernel, or the next call) become
+      // resident early; it blocks in its own griddepcontrol.wait until this grid is done.
       ptx::grid_launch_dependents();
     }
     if constexpr (kCta == 1) {
@@ -472,7 +516,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           load_stage(static_cast<int>(preloaded), kb, row_a, row_b, ptx::l2_policy(p.hint_a),
                      ptx::l2_policy(p.hint_b));
         }
-        BEAM_STAMP(2);
       }
     }
   }
@@ -485,7 +528,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   if constexpr (kCta == 2) ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) BEAM_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -498,12 +540,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
         int row_a = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
         int row_b = w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
-#ifdef BEAM_TRACE
-        if (p.debug & 2) {
-          row_a = static_cast<int>(cta_rank) * S::kBM;
-          row_b = static_cast<int>(cta_rank) * S::kBRows;
-        }
-#endif
         int kb = w.kb0;
         if (j == 0) {  // these are already in flight
           kb += static_cast<int>(preloaded);
@@ -545,25 +581,20 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;
         const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
         {
-          BEAM_ACC_BEGIN();
           const bool drained = bounded_wait(tmem_empty_bar(acc), acc_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
-          BEAM_ACC_END_T(13, 32);
           if (!drained) break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           {
-            BEAM_ACC_BEGIN();
             const bool landed = bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull);
-            BEAM_ACC_END_T(14, 32);
             if (!landed) {
               alive = false;
               break;
             }
           }
           ptx::tc_fence_after();
-          if (j == 0 && kb == w.kb0) BEAM_STAMP(3);
           ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride, idesc,
                                      kb > w.kb0 ? 1u : 0u);
           if constexpr (kCta == 1)
@@ -576,7 +607,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           }
         }
         if (alive) {
-          BEAM_STAMP(4);
           if constexpr (kCta == 1)
             ptx::umma_commit<1>(tmem_full_bar(acc));
           else
@@ -594,7 +624,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     const long long ew_chunks = (kMode == kModeGemmSilu) ? (p.ew_count + 1023) / 1024 : 0;
     const long long ew_stride = static_cast<long long>(gridDim.x) * 4;
     long long ew_chunk = static_cast<long long>(blockIdx.x) * 4 + quad;
-    if constexpr (kMode == kModeSplitK) ptx::grid_dependency_wait();  // before this thread's first global write
+    if constexpr (is_splitk_mode(kMode)) ptx::grid_dependency_wait();  // before this thread's first global write
     int ln_pending = -1;                               // LayerNorm: a unit this warp claimed ahead of its publication
     uint32_t ln_ring_count = 0;                        // LayerNorm: boxes this warp's landing ring has received
     const uint32_t ln_bufs = staging_base + quad * S::kBufsPerWarp * S::kStoreBufBytes;
@@ -638,7 +668,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       } else if constexpr (kMode == kModeLayerNorm) {
         // While the accumulator is not ready, this warp spends the time on the second pass: one unit of a
         // published panel per iteration (its staging buffers are idle: its stores have completed).
-        BEAM_ACC_BEGIN();
         const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
         bool pass2_done = false;
         for (;;) {
@@ -670,16 +699,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             }
           }
         }
-        BEAM_ACC_END(8);
       } else {
-        BEAM_ACC_BEGIN();
         ready = bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane);
-        BEAM_ACC_END(8);
       }
       if (!ready) break;
-      BEAM_ACC_BEGIN();
       ptx::tc_fence_after();
-      if (threadIdx.x == 64) BEAM_STAMP(5);
       const int row0 = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;  // first row of this CTA
       const int grow = row0 + static_cast<int>(row_in_tile);
       const int col0 = w.nt * BN;
@@ -732,9 +756,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         const int box_y = fold ? static_cast<int>(quad & 1u) * 32 : row0 + static_cast<int>(quad) * 32;
         const int box_z = fold ? 2 * w.slice + fold_half : w.slice;
         bool box_live = box_x < p.n && box_y < p.m;  // warp-uniform
-#ifdef BEAM_TRACE
-        if (p.debug & 1) box_live = false;
-#endif
         if (box_live) {
           // Before a staging buffer is rewritten, the bulk store that last read it must be done reading.
           constexpr uint32_t kBufs = S::kBufsPerWarp;
@@ -764,8 +785,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         }
       }
       // The accumulator is drained: hand it back to the MMA issuer before the slow part below.
-      BEAM_ACC_END(9);
-      if (threadIdx.x == 64) BEAM_STAMP(6);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -778,7 +797,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         // Publish this row's (mean, M2) over the tile; once this warp's parked rows have landed, fence and take
         // one of the panel's tickets (four per tile, one per epilogue warp).  The warp that draws the panel's
         // last ticket publishes it for normalisation.
-        BEAM_ACC_BEGIN();
         if (grow < p.m) p.row_part[static_cast<size_t>(grow) * p.n_tiles + w.nt] = make_float2(st_mean, st_m2);
         if (lane == 0) ptx::tma_store_wait_all<0>();
         __syncwarp();
@@ -792,7 +810,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             *reinterpret_cast<volatile int*>(p.ln_queue + kLnQueueItems + slot) = panel + 1;
           }
         }
-        BEAM_ACC_END(10);
       }
     }
     if constexpr (kMode == kModeGemmSilu) {
@@ -801,14 +818,12 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     if constexpr (kMode == kModeLayerNorm) {
       // No tiles left: keep normalising until every unit of the problem has been claimed and this warp's own
       // claim is done.  Other CTAs may still be computing, so this is a wait, and it is bounded.
-      BEAM_ACC_BEGIN();
       const uint64_t deadline = ptx::globaltimer_ns() + kWaitLimitNs;
       for (;;) {
         const int did = ln_visit<BN>(p, ln_pending, lane, ln_bufs, ln_ring_bar(quad), ln_ring_count, cta_abort, deadline);
         if (did == kLnAllDone) break;
         if (did == kLnIdle) __nanosleep(100);
       }
-      BEAM_ACC_END(12);
     }
   }
 
@@ -816,6 +831,23 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   // writing global memory) before the CTA goes away; then everyone meets and the allocating warp frees TMEM
   if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
   __syncwarp();
+  if constexpr (kMode == kModeSplitKFused) {
+    // Every CTA's partial is on its way to L2.  The grid was launched cooperatively with one work item per CTA, so
+    // all CTAs are resident and the grid-wide barrier below cannot wait for a CTA that has not started.  Every
+    // path reaches it, including a CTA whose bounded wait gave up (it then contributes whatever it has; the
+    // fault word tells the host that the result is invalid).  After the barrier each CTA reduces its share.
+    __threadfence();
+    cooperative_groups::this_grid().sync();
+    const int planes = p.slices * (fold ? 2 : 1);
+    const long long units = static_cast<long long>(p.m) * (p.n >> 2);  // float4 groups of the output
+    const long long u0 = units * blockIdx.x / gridDim.x;
+    const long long u1 = units * (blockIdx.x + 1) / gridDim.x;
+    float4* sums = reinterpret_cast<float4*>(smem_gen);  // the operand ring is idle by now
+    if (u1 - u0 <= kReduceUnitsPerPass)
+      splitk_reduce_share<1, 32>(p.scratch, p.c, p.m, p.n, planes, u0, u1, sums);
+    else
+      splitk_reduce_share<4, 8>(p.scratch, p.c, p.m, p.n, planes, u0, u1, sums);
+  }
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();
   __syncthreads();
@@ -824,14 +856,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     ptx::tc_fence_after();
     ptx::tmem_dealloc<kCta>(tmem_base, S::kTmemCols);
   }
-  if (threadIdx.x == 0) BEAM_STAMP(7);
 }
 
-// Second kernel of split-K: C[r][c] = fp16( sum over slices, in a fixed order, of partial[s][r][c] ).
-// A block owns one row x 128 columns; thread (g, q) adds the slices of group g (a contiguous range,
-// ascending) for 4 columns, then the 8 group sums are added in ascending g.  The association order
-// depends only on the slice count, never on timing, so results are bitwise reproducible.
-constexpr int kReduceGroups = 8;
+// Second kernel of the two-kernel split-K path: the same fixed-order sum with a block per row x 128 columns;
+// thread (g, q) adds the slices of group g (a contiguous range, ascending) for 4 columns, then the 8 group
+// sums are added in ascending g.
 static __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial,
                                                                    __half* __restrict__ c, int m, int n,
                                                                    int slices) {

@@ -19,19 +19,6 @@
 
 namespace beam {
 
-#ifdef BEAM_TRACE
-// timeline of CTA 0 (diagnostic build): tagged time stamps appended to a region behind the per-CTA slots
-#define BEAM_TL(base, idx, tag)                                                                             \
-  do {                                                                                                      \
-    if (p.trace && blockIdx.x == 0 && (idx) < 1024u)                                                        \
-      p.trace[148 * 16 + (base) + (idx)++] = (static_cast<unsigned long long>(tag) << 56) | (ptx::globaltimer_ns() & 0xFFFFFFFFFFFFull); \
-  } while (0)
-#else
-#define BEAM_TL(base, idx, tag) \
-  do {                          \
-  } while (0)
-#endif
-
 template <int kStages>
 struct WideShape {
   static constexpr int kBM = 128;
@@ -66,7 +53,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) BEAM_STAMP(0);
   const uint32_t cta_rank = ptx::cluster_ctarank();
   const bool leader = cta_rank == 0;
   Walk walk;
@@ -119,7 +105,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
-      [[maybe_unused]] uint32_t tl_p = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
@@ -137,7 +122,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
             alive = false;
             break;
           }
-          BEAM_TL(2048, tl_p, 21);
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
           const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
           ptx::tma_load_2d_pair_hint(smem_box(s, 0), &p.tm_a, lead_bar, kb * S::kBK, r0, pol_a);
@@ -152,7 +136,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc_f16_f32(256, S::kHalfN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       uint32_t it = 0;
-      [[maybe_unused]] uint32_t tl_m = 0;
       bool alive = true;
       WorkItem w;
       auto issue_half = [&](int s, int h, bool first_kb) {
@@ -166,9 +149,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       // A group of k-blocks issued half-major: half 0 of each (waiting for its bytes), then, after `between`,
       // half 1 of each, which is also where their stages are released.
       auto wait_landed = [&](uint32_t k) {
-        BEAM_ACC_BEGIN();
         const bool landed = bounded_wait(full_bar(k % kStages), (k / kStages) & 1u, cta_abort, p.status, kFaultMmaWaitFull);
-        BEAM_ACC_END_T(14, 32);
         if (landed) ptx::tc_fence_after();
         return landed;
       };
@@ -181,28 +162,21 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         const int lead_in = num_kb < p.lead_in ? num_kb : p.lead_in;
         const int lead_out = (num_kb - lead_in) < p.lead_out ? (num_kb - lead_in) : p.lead_out;
         {
-          BEAM_ACC_BEGIN();
           const bool ok0 = bounded_wait(tmem_empty_bar(0), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
-          BEAM_ACC_END_T(13, 32);
           if (!ok0) break;
         }
-        BEAM_TL(0, tl_m, 1);
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in && alive; ++g) {
           alive = wait_landed(it + static_cast<uint32_t>(g));
           if (!alive) break;
-          BEAM_TL(0, tl_m, 2);
           issue_half((it + static_cast<uint32_t>(g)) % kStages, 0, g == 0);
         }
         if (!alive) break;
         if (lead_in == num_kb) ptx::umma_commit_pair_both(tmem_full_bar(0), 0x3);  // half 0 is complete already
         {
-          BEAM_ACC_BEGIN();
           const bool ok1 = bounded_wait(tmem_empty_bar(1), tile_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc);
-          BEAM_ACC_END_T(12, 32);
           if (!ok1) break;
         }
-        BEAM_TL(0, tl_m, 3);
         ptx::tc_fence_after();
         for (int g = 0; g < lead_in; ++g) {
           const int s = (it + static_cast<uint32_t>(g)) % kStages;
@@ -214,7 +188,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           alive = wait_landed(it);
           if (!alive) break;
           const int s = it % kStages;
-          BEAM_TL(0, tl_m, 4);
           if (kTall) {
             // both halves multiply by the same B: alternate so that neighbouring UMMAs share the operand
             const uint64_t a0_desc = ptx::umma_desc_k_sw128(smem_a(s, 0));
@@ -244,7 +217,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           for (int g = 0; g < lead_out && alive; ++g) {
             alive = wait_landed(it + static_cast<uint32_t>(g));
             if (!alive) break;
-            BEAM_TL(0, tl_m, 6);
             issue_half((it + static_cast<uint32_t>(g)) % kStages, 0, false);
           }
           if (!alive) break;
@@ -257,7 +229,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           it += static_cast<uint32_t>(lead_out);
         }
         ptx::umma_commit_pair_both(tmem_full_bar(1), 0x3);
-        BEAM_TL(0, tl_m, 5);
       }
     }
   } else {
@@ -273,18 +244,13 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     auto out_row = [&](int i) { return kTall ? (i >> 1) * 256 : 0; };
     auto out_col = [&](int i) { return kTall ? static_cast<int>(col_half) * 128 + (i & 1) * 64 : chunk_col(i); };
     uint32_t store_count = 0;
-    [[maybe_unused]] uint32_t tl_e = 0;
     WorkItem w;
     for (int j = 0; work_item<kModeGemm>(p, walk, j, num_kb, w); ++j) {
       {
-        BEAM_ACC_BEGIN();
         const bool ready = bounded_wait_warp(tmem_full_bar(0), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
                                              kFaultEpilogueWait, lane);
-        BEAM_ACC_END(8);
         if (!ready) break;
       }
-      BEAM_ACC_BEGIN();
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 11);
       ptx::tc_fence_after();
       const int row0 = w.mt * (kTall ? 512 : 256) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
       const int tile_col0 = w.nt * (kTall ? 256 : S::kTileN);
@@ -329,19 +295,14 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           ++store_count;
         }
       };
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 16);
       load_chunk(0, va0, va1);
       load_chunk(1, vb0, vb1);
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 17);
       ptx::tmem_ld_wait();
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 18);
       release_half(0);
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 12);
       round_chunk(va0, va1);
       if (!bounded_wait_warp(tmem_full_bar(1), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
                              kFaultEpilogueWait, lane))
         break;
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 13);
       ptx::tc_fence_after();
       load_chunk(2, va0, va1);
       stage_and_store(0);
@@ -349,14 +310,11 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       load_chunk(3, vb0, vb1);
       ptx::tmem_ld_wait();
       release_half(1);
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 14);
       stage_and_store(1);
       round_chunk(va0, va1);
       stage_and_store(2);
       round_chunk(vb0, vb1);
       stage_and_store(3);
-      if (threadIdx.x == 64) BEAM_TL(1024, tl_e, 15);
-      BEAM_ACC_END(9);
     }
   }
 
@@ -370,7 +328,6 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     ptx::tc_fence_after();
     ptx::tmem_dealloc<2>(tmem_base, S::kTmemCols);
   }
-  if (threadIdx.x == 0) BEAM_STAMP(7);
 }
 
 }  // namespace beam

@@ -32,6 +32,41 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// A descriptor is a pure function of (base, extents, pitch, box, type, swizzle), and callers come back with the
+// same tensors call after call, so each host thread keeps the last few it encoded: a hit costs a short compare
+// instead of a driver call.  (Base pointers are unique across devices under unified addressing.)
+struct TmapKey {
+  const void* base;
+  uint64_t d0, d1, d2, pitch;
+  uint32_t box0, box1, kind;
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapSlots = 32;
+thread_local TmapSlot t_tmaps[kTmapSlots];
+thread_local unsigned t_tmap_next = 0;
+
+bool tmap_lookup(const TmapKey& key, CUtensorMap* out) {
+  for (int i = 0; i < kTmapSlots; ++i) {
+    const TmapSlot& s = t_tmaps[i];
+    if (s.used && s.key.base == key.base && s.key.d0 == key.d0 && s.key.d1 == key.d1 && s.key.d2 == key.d2 &&
+        s.key.pitch == key.pitch && s.key.box0 == key.box0 && s.key.box1 == key.box1 && s.key.kind == key.kind) {
+      std::memcpy(out, &s.map, sizeof(CUtensorMap));
+      return true;
+    }
+  }
+  return false;
+}
+void tmap_remember(const TmapKey& key, const CUtensorMap* map) {
+  TmapSlot& s = t_tmaps[t_tmap_next++ % kTmapSlots];
+  s.key = key;
+  std::memcpy(&s.map, map, sizeof(CUtensorMap));
+  s.used = true;
+}
+
 }  // namespace
 
 void note_cuda_error(cudaError_t e, const char* where) {
@@ -49,9 +84,9 @@ DeviceCtx* current_device_ctx(int* err) {
     return nullptr;
   }
   DeviceCtx* c = &g_ctx[dev];
-  if (c->ok) return c;
+  if (c->ok.load(std::memory_order_acquire)) return c;
   std::lock_guard<std::mutex> lock(g_ctx_mutex);
-  if (c->ok) return c;
+  if (c->ok.load(std::memory_order_acquire)) return c;
   cudaDeviceProp prop;
   e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) {
@@ -71,6 +106,7 @@ DeviceCtx* current_device_ctx(int* err) {
   c->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
   c->cc_major = prop.major;
   c->cc_minor = prop.minor;
+  c->cooperative_launch = prop.cooperativeLaunch != 0;
   e = cudaMalloc(&c->status_word, 256);
   if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, 256);
   if (e != cudaSuccess) {
@@ -79,12 +115,15 @@ DeviceCtx* current_device_ctx(int* err) {
     *err = BEAM_ERR_CUDA;
     return nullptr;
   }
-  c->ok = true;
+  c->ok.store(true, std::memory_order_release);
   return c;
 }
 
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                    uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  const TmapKey key = {base, cols, rows, 0, ld, box_cols, box_rows,
+                       static_cast<uint32_t>(elem_bytes) | (swizzle128 ? 0x100u : 0u)};
+  if (tmap_lookup(key, out)) return BEAM_OK;
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return BEAM_ERR_TENSORMAP;
   const cuuint64_t gdim[2] = {cols, rows};
@@ -100,12 +139,15 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
                   static_cast<int>(r));
     return BEAM_ERR_TENSORMAP;
   }
+  tmap_remember(key, out);
   return BEAM_OK;
 }
 
 // 3-D row-major fp32 tensor [planes][rows][cols] (dense), box = 1 x box_rows x box_cols, 128-byte swizzle.
 int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                        uint32_t box_rows, uint32_t box_cols) {
+  const TmapKey key = {base, cols, rows, planes, 0, box_cols, box_rows, 0x1000u};
+  if (tmap_lookup(key, out)) return BEAM_OK;
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return BEAM_ERR_TENSORMAP;
   const cuuint64_t gdim[3] = {cols, rows, planes};
@@ -120,6 +162,7 @@ int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint
                   static_cast<int>(r));
     return BEAM_ERR_TENSORMAP;
   }
+  tmap_remember(key, out);
   return BEAM_OK;
 }
 

@@ -5,6 +5,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 
@@ -18,7 +19,9 @@ struct DeviceCtx {
   int max_smem_optin = 0;
   int cc_major = 0, cc_minor = 0;
   int* status_word = nullptr;  // device memory, one int, zero while healthy
-  bool ok = false;
+  bool cooperative_launch = false;             // the device places cooperative grids
+  std::atomic<bool> coop_without_pdl{false};   // set once a cooperative grid was refused as a programmatic dependent
+  std::atomic<bool> ok{false};                 // published last (release); readers acquire
 };
 
 // Returns the context of the CUDA device that is current on the calling thread, creating it

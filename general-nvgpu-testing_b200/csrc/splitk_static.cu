@@ -116,10 +116,6 @@ int launch_partials(const StaticSetup& s, const void* A, const void* B, void* C,
   p.ew_out = nullptr;
   p.ew_count = 0;
   p.status = fault_word;
-#ifdef BEAM_TRACE
-  p.trace = nullptr;
-  p.debug = 0;
-#endif
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * slices;
   const int ctas = items < s.sm_count ? static_cast<int>(items) : s.sm_count;
   cudaLaunchConfig_t cfg = {};
@@ -152,7 +148,10 @@ extern "C" BEAM_API int beam_gemmrc_splitk_noalloc(const void* A, const void* B,
   st = setup_device(dev, &s);
   if (st != BEAM_OK) return st;
 
-  // Same tile choice and split rule as the workspace entry point, computed without the library context.
+  // Tile choice and split rule of the workspace entry point's two-kernel form, computed without the library
+  // context, with one difference: problems with M, N <= 64 are not folded here (they run the plain 64-wide tile,
+  // one plane per slice), so for those shapes this entry is slower than the workspace one and its sum is
+  // associated differently (equal within the parity tolerance, not bit for bit).
   const int bn = splitk_tile_n(n, 0);
   const int num_kb = (k + 63) / 64;
   int slices = split_k_slices;

@@ -25,7 +25,7 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 constexpr uint32_t kSpinSuspendNs = 4000u;
 
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort,
-                                             int* status_word, int fault) {
+                                             int* status_word, int fault, uint64_t limit_ns = kWaitLimitNs) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
@@ -36,7 +36,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
       const uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *cta_abort = 1;
         if (status_word) atomicCAS(status_word, 0, fault);
         return false;
@@ -51,7 +51,8 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
 constexpr uint32_t kSuspendNs = 50000u;
 
 __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, volatile int* cta_abort,
-                                                  int* status_word, int fault, uint32_t lane) {
+                                                  int* status_word, int fault, uint32_t lane,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
   int ok = 1;
   if (lane == 0) {
     if (!ptx::mbar_try_wait(bar, parity)) {
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity,
           const uint64_t now = ptx::globaltimer_ns();
           if (t0 == 0) {
             t0 = now;
-          } else if (now - t0 > kWaitLimitNs) {
+          } else if (now - t0 > limit_ns) {
             *cta_abort = 1;
             if (status_word) atomicCAS(status_word, 0, fault);
             ok = 0;

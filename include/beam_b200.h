@@ -73,6 +73,10 @@ typedef struct beam_gemm_cfg {
 /* beam_gemmrc_fp16 only: A, B and C hold bf16 instead of fp16 (same kernels; fp32 accumulation, one rounding to
  * bf16).  The reference reaches bf16 only through its cuBLAS comparator (cuda/cublas.cc:106-108). */
 #define BEAM_FLAG_BF16 2
+/* Split-K only.  Run the call as two kernels (partials, then a reduction kernel) even where the one-kernel form
+ * applies.  Both forms add the partials in the same order and agree bit for bit; this flag exists for comparison
+ * and for callers that must not launch cooperative grids. */
+#define BEAM_FLAG_SPLITK_TWO_KERNELS 4
 
 BEAM_API const char* beam_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
@@ -137,8 +141,14 @@ BEAM_API size_t beam_gemmrc_splitk_workspace_bytes(int m, int n, int k, int tile
  * cutlass_gemmrc_splitk.cu:44-57), which models the 108 SMs of an A100. */
 BEAM_API int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n);
 
+/* How a split-K call with these arguments runs on the current device: info[0] = tile N, info[1] = K slices,
+ * info[2] = 1 if the problem runs folded (M, N <= 64: two k-blocks per UMMA), info[3] = kernels per call (1 or 2),
+ * info[4] = 1 if the call's first kernel is a programmatic dependent launch.  info must hold 5 ints. */
+BEAM_API int beam_gemmrc_splitk_describe(int m, int n, int k, int tile_n, int split_k_slices, int flags, int* info);
+
 /* Generic split-K entry: cfg->tile_n (0 = default), cfg->split_k_slices (0 = heuristic) and cfg->flags
- * (BEAM_FLAG_INPUTS_STABLE) are honoured; cfg may be NULL.  The two registry names below are presets. */
+ * (BEAM_FLAG_INPUTS_STABLE, BEAM_FLAG_SPLITK_TWO_KERNELS) are honoured; cfg may be NULL.  The two registry names
+ * below are presets. */
 BEAM_API int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n, int k,
                                      const beam_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
                                      void* stream);
@@ -146,8 +156,11 @@ BEAM_API int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int 
 /* Registry name `cutlass_gemmrc_splitk` — replaces entry_cutlass_gemmrc_splitk (cuda/cutlass_kernels/
  * cutlass_gemmrc_splitk.cu:59-105).  K is cut into `split_k_slices` contiguous runs of 64-wide
  * k-blocks; each CTA accumulates one slice of one tile in TMEM and writes an fp32 partial to
- * `workspace`; a second kernel adds the partials of every output in a fixed order that depends only
- * on the slice count (bitwise reproducible) and rounds once to fp16.  A split factor outside
+ * `workspace`; the partials of every output are then added in a fixed order that depends only on the
+ * slice count (bitwise reproducible) and rounded once to fp16.  When every (tile, slice) fits on the
+ * device at once (tiles x slices <= SM count, which the heuristic guarantees) this is ONE cooperative
+ * kernel: after a grid-wide barrier each CTA sums its share of the output; otherwise a second kernel does
+ * the sum.  The reference always launches two kernels (gemm_splitk_parallel + reduce).  A split factor outside
  * [1, K/64] falls back to the heuristic, as the reference does for values outside (0, K/32) (:77-94).
  * The reference keeps a hidden grow-only cudaMalloc'd buffer (:31-42); here the caller owns it. */
 BEAM_API int beam_cutlass_gemmrc_splitk(const void* A, const void* B, void* C, int m, int n, int k, int split_k_slices,

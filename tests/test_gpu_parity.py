@@ -220,6 +220,7 @@ SPLITK_CASES = [
     (128, 256, 65536, 128, 0), (128, 256, 65536, 128, 4), (128, 256, 65536, 128, 64), (128, 256, 65536, 256, 32),
     (128, 256, 65536, 64, 16), (64, 64, 131072, 64, 0), (64, 64, 131072, 64, 8), (64, 64, 131072, 64, 64),
     (40, 72, 1096, 64, 3), (200, 136, 2048, 128, 5),
+    (128, 256, 65536, 64, 64),  # 4 tiles x 64 slices = 256 work items: more than the SMs, so two kernels
 ]
 
 
@@ -241,6 +242,37 @@ def test_config3_splitk(beam, oracle_mod, m, n, k, tile_n, slices):
     c2 = torch.zeros_like(c)
     beam.cutlass_gemmrc_splitk_spec(da, db, c2, shape_threadblock=[128, tile_n], split_k_slices=slices)
     assert torch.equal(c, c2), "split-K must be bitwise reproducible"
+    # The call runs as one cooperative kernel whenever its (tile, slice) items fit on the device at once; forced
+    # into the partials + reduction pair of kernels it must give the same bits (same association of the sum).
+    plan = beam.splitk_describe(m, n, k, tile_n, slices)
+    items = -(-m // 128) * -(-n // plan["tile_n"]) * plan["slices"]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert plan["kernels_per_call"] == (1 if items <= sms else 2), plan
+    c3 = torch.zeros_like(c)
+    beam.cutlass_gemmrc_splitk_spec(da, db, c3, shape_threadblock=[128, tile_n], split_k_slices=slices,
+                                    two_kernels=True)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert beam.splitk_describe(m, n, k, tile_n, slices, two_kernels=True)["kernels_per_call"] == 2
+    assert torch.equal(c, c3), "one-kernel and two-kernel split-K must agree bit for bit"
+
+
+@pytest.mark.parametrize("m,n,k,tile_n,slices", [(128, 256, 16384, 128, 32), (64, 64, 32768, 64, 0),
+                                                 (72, 200, 4096, 64, 7)])
+def test_splitk_exact_on_integer_inputs(beam, oracle_mod, m, n, k, tile_n, slices):
+    """With small integer inputs every product and every partial sum is exact in fp32, so the order of the
+    additions does not matter and the kernel must reproduce the slice-ordered CPU restatement bit for bit."""
+    rng = np.random.Generator(np.random.PCG64(77 + slices))
+    a = rng.integers(-2, 3, (m, k)).astype(np.float16)
+    b = rng.integers(-2, 3, (n, k)).astype(np.float16)
+    s = beam.splitk_describe(m, n, k, tile_n, slices)["slices"]
+    want = oracle_mod.gemmrc_splitk(a, b, s)
+    assert np.array_equal(want, oracle_mod.gemmrc(a, b))
+    c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc_splitk_spec(_dev(a), _dev(b), c, shape_threadblock=[128, tile_n], split_k_slices=slices)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    assert np.array_equal(c.cpu().numpy(), want)
 
 
 def test_splitk_default_entry(beam, oracle_mod):

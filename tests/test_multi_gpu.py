@@ -1,6 +1,7 @@
 """Two-GPU test of the fused GEMM + all-gather and of the row-sharded GEMM + LayerNorm (pytest -m gpu on a box with at least two GPUs; skipped otherwise).
 Each rank multiplies its row block and the kernel's epilogue stores every tile into both ranks' gathered buffers
-through peer-mapped (symmetric) memory; the result must equal the plain sharded GEMM followed by an NCCL all-gather."""
+through peer-mapped (symmetric) memory; the result must equal the plain sharded GEMM followed by an NCCL all-gather
+and, on the small shapes, the CPU oracle's GEMM of every rank's rows."""
 import os
 import socket
 import sys
@@ -29,6 +30,9 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
+        import numpy as np
+        sys.path.insert(0, here)
+        import oracle  # the CPU checker (built by the parent process before the ranks start)
         import beam
         from beam.sharded import GatheredC, all_gather_rows, gemmrc_allgather
         for (m_local, n, k, knobs) in ((512, 1024, 512, {}), (300, 776, 264, {"tile_n": 256, "cta_pair": 2}),
@@ -45,6 +49,12 @@ def _worker(rank, world, port, out_dir):
             got = gemmrc_allgather(a, b, gathered, **knobs)
             torch.cuda.synchronize()
             assert torch.equal(got, want), "rank %d shape %s" % (rank, (m_local, n, k))
+            if m_local <= 512:
+                # against the CPU oracle too: every rank's block of the gathered result, the peers' blocks included
+                a_all = [(torch.randn(m_local, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(
+                    100 + r)) * 0.1).half().cpu().numpy() for r in range(world)]
+                ref = np.concatenate([oracle.gemmrc(ar, b.cpu().numpy()) for ar in a_all], axis=0)
+                assert oracle.floored_max_rel(got.cpu().numpy(), ref) <= oracle.REL_TOL, "oracle, rank %d" % rank
         # Row-sharded GEMM + LayerNorm: the statistics are per row, so the gathered result of the two ranks must be
         # what one GPU computes for all rows.
         from beam.sharded import sharded_gemm_layernorm
@@ -69,7 +79,7 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_fused_gemm_allgather_two_gpus(tmp_path, built_library):
+def test_fused_gemm_allgather_two_gpus(tmp_path, built_library, oracle_mod):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2

@@ -54,7 +54,8 @@ def test_noalloc_matches_workspace_entry_twice_in_a_row(built_library, oracle_mo
         assert st == 0
         torch.cuda.synchronize()
         assert int(fault.item()) == 0
-        # same kernels, same reduction order: equal within the parity tolerance (in fact bit for bit)
+        # same arithmetic: equal within the parity tolerance (bit for bit for the 128 x 256 cases; the 64 x 64 case
+        # runs folded in the workspace entry and unfolded here, which associates the sum differently)
         assert oracle_mod.floored_max_rel(got.cpu().numpy(), want.cpu().numpy()) <= oracle_mod.REL_TOL
         ref = oracle_mod.gemmrc(a.cpu().numpy(), b.cpu().numpy())
         assert oracle_mod.floored_max_rel(got.cpu().numpy(), ref) <= oracle_mod.REL_TOL
