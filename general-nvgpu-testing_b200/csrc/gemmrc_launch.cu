@@ -181,6 +181,11 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     --cfg.numAttrs;
     e = cudaLaunchKernelEx(&cfg, kernel, p);
   }
+  if (kMode == kModeSplitKFused && e == cudaErrorCooperativeLaunchTooLarge) {
+    // fewer CTAs fit at once than the device's SM count promised (a partitioned GPU): the caller runs two kernels
+    (void)cudaGetLastError();
+    return BEAM_ERR_UNSUPPORTED;
+  }
   BEAM_CUDA_TRY(e, "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
@@ -478,9 +483,14 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   if (splitk_one_kernel(ctx, m, n, bn, s, flags)) {
     // One kernel: partials, a grid-wide barrier, then every CTA sums its share of the output (same order as the
     // reduction kernel below, so the two paths agree bit for bit).
-    if (bn == 64) return launch_instance<64, 8, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
-    if (bn == 128) return launch_instance<128, 6, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
-    return launch_instance<256, 4, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    if (bn == 64)
+      st = launch_instance<64, 8, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    else if (bn == 128)
+      st = launch_instance<128, 6, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    else
+      st = launch_instance<256, 4, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+    if (st != BEAM_ERR_UNSUPPORTED) return st;
+    ctx->cooperative_launch = false;  // the grid does not fit at once on this device: two kernels from now on
   }
   if (bn == 64)
     st = launch_instance<64, 8, 1, kModeSplitK>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);

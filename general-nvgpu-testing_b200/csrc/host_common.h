@@ -19,7 +19,7 @@ struct DeviceCtx {
   int max_smem_optin = 0;
   int cc_major = 0, cc_minor = 0;
   int* status_word = nullptr;  // device memory, one int, zero while healthy
-  bool cooperative_launch = false;             // the device places cooperative grids
+  std::atomic<bool> cooperative_launch{false}; // the device places cooperative grids of one CTA per SM
   std::atomic<bool> coop_without_pdl{false};   // set once a cooperative grid was refused as a programmatic dependent
   std::atomic<bool> ok{false};                 // published last (release); readers acquire
 };
