@@ -59,7 +59,7 @@ class beam_gemm_cfg(ctypes.Structure):
         ("l2_hints", ctypes.c_int),
         ("flags", ctypes.c_int),
         ("tile_m", ctypes.c_int),
-        ("reserved", ctypes.c_int * 1),
+        ("tiles_in_flight", ctypes.c_int),
     ]
 
 
@@ -205,7 +205,7 @@ def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 6
     _run("beam_cutlass_gemmrc_spec", a, b, c, tbm, tbn, wm, wn)
 
 
-def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, tile_m=0):
+def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, tile_m=0, tiles_in_flight=0):
     """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over.  The three tensors may
     be bfloat16 instead of float16 (all three alike)."""
     m, n, k = _check_abc(a, b, c, allow_bf16=True)
@@ -213,7 +213,7 @@ def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hi
         raise TypeError("a, b, c must share one dtype")
     flags = 2 if a.dtype == torch.bfloat16 else 0
     cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), flags,
-                        int(tile_m))
+                        int(tile_m), int(tiles_in_flight))
     L = _load()
     with torch.cuda.device(a.device):
         st = L.beam_gemmrc_fp16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, ctypes.byref(cfg), _stream(a))
@@ -223,14 +223,25 @@ def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hi
 
 FLAG_INPUTS_STABLE = 1
 FLAG_SPLITK_TWO_KERNELS = 4
+FLAG_SPLITK_ONE_KERNEL = 8
 
 
-def splitk_describe(m, n, k, tile_n=0, split_k_slices=0, inputs_stable=False, two_kernels=False):
+def _splitk_flags(inputs_stable, two_kernels):
+    """two_kernels: None = the library decides, True = partials + reduction kernels, False = one kernel where it applies."""
+    flags = FLAG_INPUTS_STABLE if inputs_stable else 0
+    if two_kernels is True:
+        flags |= FLAG_SPLITK_TWO_KERNELS
+    elif two_kernels is False:
+        flags |= FLAG_SPLITK_ONE_KERNEL
+    return flags
+
+
+def splitk_describe(m, n, k, tile_n=0, split_k_slices=0, inputs_stable=False, two_kernels=None):
     """How a split-K call with these arguments runs on the current device: a dict with the tile N, the number of K
     slices, whether the problem runs folded, the kernels per call (1 or 2) and whether the first kernel is a
     programmatic dependent launch."""
     info = (ctypes.c_int * 5)()
-    flags = (FLAG_INPUTS_STABLE if inputs_stable else 0) | (FLAG_SPLITK_TWO_KERNELS if two_kernels else 0)
+    flags = _splitk_flags(inputs_stable, two_kernels)
     st = _load().beam_gemmrc_splitk_describe(int(m), int(n), int(k), int(tile_n), int(split_k_slices), flags, info)
     if st != BEAM_OK:
         _raise(st, "beam_gemmrc_splitk_describe")
@@ -238,10 +249,10 @@ def splitk_describe(m, n, k, tile_n=0, split_k_slices=0, inputs_stable=False, tw
             "programmatic_dependent_launch": bool(info[4])}
 
 
-def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable, two_kernels=False):
+def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable, two_kernels=None):
     m, n, k = _check_abc(a, b, c)
     L = _load()
-    flags = (FLAG_INPUTS_STABLE if inputs_stable else 0) | (FLAG_SPLITK_TWO_KERNELS if two_kernels else 0)
+    flags = _splitk_flags(inputs_stable, two_kernels)
     cfg = beam_gemm_cfg(int(tile_n), 0, 0, 0, int(split_k_slices), 0, 0, flags)
     with torch.cuda.device(a.device):
         nbytes = L.beam_gemmrc_splitk_workspace_bytes(m, n, k, int(tile_n), int(split_k_slices))
@@ -254,17 +265,18 @@ def _splitk(a, b, c, tile_n, split_k_slices, inputs_stable, two_kernels=False):
         _raise(st, "beam_gemmrc_splitk_fp16")
 
 
-def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0, inputs_stable=False, two_kernels=False):
+def cutlass_gemmrc_splitk(a, b, c, split_k_slices=0, inputs_stable=False, two_kernels=None):
     """Split-K c = a @ b.T for small M, N and huge K; fp32 partials summed in a fixed order (bitwise
     reproducible).  split_k_slices = 0 lets the library choose (slot of cutlass_gemmrc_splitk.cu:59-105).
     inputs_stable=True promises that a and b are not outputs of the kernel just before this call on the
     stream, which lets back-to-back calls overlap (BEAM_FLAG_INPUTS_STABLE).  two_kernels=True forces the
-    partials-then-reduction pair of kernels where the library would run the call as one kernel (same bits)."""
+    partials-then-reduction pair of kernels where the library would run the call as one kernel, False the one-kernel
+    form where the library would launch two (same bits either way); None leaves the choice to the library."""
     _splitk(a, b, c, 0, split_k_slices, inputs_stable, two_kernels)
 
 
 def cutlass_gemmrc_splitk_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 64], split_k_slices=0,
-                               inputs_stable=False, two_kernels=False):
+                               inputs_stable=False, two_kernels=None):
     """Split-K with the tile's N taken from shape_threadblock[1] (64, 128 or 256); shape_warp is accepted for
     signature compatibility (cuda/cutlass_kernels/main.cc:137-141) and ignored."""
     tbm, tbn = _pair(shape_threadblock, "shape_threadblock")

@@ -54,6 +54,8 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.l2_hints = cfg->l2_hints;
     plan.bf16 = (cfg->flags & BEAM_FLAG_BF16) ? 1 : 0;
     plan.tile_m = cfg->tile_m;
+    plan.tiles_in_flight = cfg->tiles_in_flight;
+    if (plan.tiles_in_flight < 0 || plan.tiles_in_flight > 2) return BEAM_ERR_INVALID_ARG;
     if (plan.tile_m != 0 && plan.tile_m != 512) return BEAM_ERR_INVALID_ARG;
     if (cfg->flags & ~(BEAM_FLAG_BF16)) return BEAM_ERR_INVALID_ARG;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
@@ -141,7 +143,9 @@ int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n,
     slices = cfg->split_k_slices;
     flags = cfg->flags;
     if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return BEAM_ERR_UNSUPPORTED;
-    if (flags & ~(BEAM_FLAG_INPUTS_STABLE | BEAM_FLAG_SPLITK_TWO_KERNELS)) return BEAM_ERR_INVALID_ARG;
+    if (flags & ~(BEAM_FLAG_INPUTS_STABLE | BEAM_FLAG_SPLITK_TWO_KERNELS | BEAM_FLAG_SPLITK_ONE_KERNEL))
+      return BEAM_ERR_INVALID_ARG;
+    if ((flags & BEAM_FLAG_SPLITK_TWO_KERNELS) && (flags & BEAM_FLAG_SPLITK_ONE_KERNEL)) return BEAM_ERR_INVALID_ARG;
   }
   return launch_splitk(A, B, C, m, n, k, tile_n, slices, workspace, workspace_bytes,
                        static_cast<cudaStream_t>(stream), flags);

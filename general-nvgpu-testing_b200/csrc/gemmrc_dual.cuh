@@ -1,0 +1,313 @@
+// The N = 128 tile families (128 x 128 per CTA, 256 x 128 per CTA pair) with TWO output tiles in flight.
+//
+// A tcgen05.mma of N = 128, K = 16 is 64 clocks of tensor-pipe work, but consecutive UMMAs into the SAME
+// accumulator retire only about every 120 clocks: the next one needs the previous result.  With one tile per
+// CTA every instruction of the main loop targets the same accumulator, and the pipe idles for nearly half of
+// the time.  Here a CTA (pair) works on two neighbouring output tiles at once: a shared-memory stage carries one
+// k-block of both tiles (A and B boxes of each, loaded independently), and the issuer alternates, instruction by
+// instruction, between the two tiles' accumulators, so that an accumulator is revisited only every second
+// instruction.  TMEM holds four 128-column accumulators: two being computed, two being drained by the epilogue.
+//
+// Roles, barriers, staging and the TMA-store epilogue are those of gemmrc_umma_kernel in GEMM mode.  The two
+// tiles of a work item are consecutive in the grouped raster (same N tile, adjacent M tiles inside a group), so
+// their B boxes are the same lines in L2.  When the tile count is odd the last item's second tile does not exist:
+// its loads fall outside the tensors (zero fill), its products are zeros and its stores are skipped.
+#pragma once
+
+#include "gemmrc_umma.cuh"
+
+namespace beam {
+
+template <int kStages, int kCta>
+struct DualShape {
+  static constexpr int kBN = 128;
+  static constexpr int kBM = 128;
+  static constexpr int kBK = 64;
+  static constexpr int kBRows = kBN / kCta;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = kBRows * kBK * 2;
+  static constexpr int kTileBytes = kABytes + kBBytes;  // one tile's k-block in one CTA
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kTmemCols = 4 * kBN;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kStoreBufBytes = 32 * 128;
+  static constexpr int kBufsPerWarp = 2;
+  static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;
+  static constexpr int kThreads = 192;
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
+  static_assert((2 * kStages + 4) * 8 + 32 <= kBarBytes, "barrier block too small");
+  static_assert(kTileBytes % 1024 == 0, "tile buffers must keep the 1024-byte alignment of the swizzle atom");
+};
+
+// Tile `t` of the grouped raster (see work_item in gemmrc_umma.cuh); a tile index past the end maps to the row of
+// tiles below the matrix, which loads as zeros and stores nothing.
+__device__ __forceinline__ void dual_tile_coords(const GemmParams& p, int t, int& mt, int& nt) {
+  if (t >= p.m_tiles * p.n_tiles) {
+    mt = p.m_tiles;
+    nt = 0;
+    return;
+  }
+  const int per_group = p.group_m * p.n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * p.group_m;
+  const int rows = min(p.group_m, p.m_tiles - first_m);
+  const int r = t - g * per_group;
+  mt = first_m + r % rows;
+  nt = r / rows;
+}
+
+namespace ptx {
+// One 64-wide k-block of two tiles: eight UMMAs (K = 16 each), alternating between the two accumulators.
+template <int kCta>
+__device__ __forceinline__ void umma_f16_kblock_two_tiles(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t b0,
+                                                          uint64_t a1, uint64_t b1, uint32_t idesc,
+                                                          uint32_t accumulate_first) {
+#define BEAM_DUAL_BODY(CG)                                                  \
+  asm volatile(                                                             \
+      "{\n\t"                                                               \
+      ".reg .pred p, q;\n\t"                                                \
+      ".reg .b64 a, b;\n\t"                                                 \
+      "setp.ne.b32 p, %7, 0;\n\t"                                           \
+      "setp.eq.b32 q, 0, 0;\n\t"                                            \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%0], %2, %3, %6, p;\n\t"    \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], %4, %5, %6, p;\n\t"    \
+      "add.u64 a, %2, 2;\n\t"                                               \
+      "add.u64 b, %3, 2;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%0], a, b, %6, q;\n\t"      \
+      "add.u64 a, %4, 2;\n\t"                                               \
+      "add.u64 b, %5, 2;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a, b, %6, q;\n\t"      \
+      "add.u64 a, %2, 4;\n\t"                                               \
+      "add.u64 b, %3, 4;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%0], a, b, %6, q;\n\t"      \
+      "add.u64 a, %4, 4;\n\t"                                               \
+      "add.u64 b, %5, 4;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a, b, %6, q;\n\t"      \
+      "add.u64 a, %2, 6;\n\t"                                               \
+      "add.u64 b, %3, 6;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%0], a, b, %6, q;\n\t"      \
+      "add.u64 a, %4, 6;\n\t"                                               \
+      "add.u64 b, %5, 6;\n\t"                                               \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a, b, %6, q;\n\t"      \
+      "}\n" ::"r"(d0),                                                      \
+      "r"(d1), "l"(a0), "l"(b0), "l"(a1), "l"(b1), "r"(idesc), "r"(accumulate_first)                          \
+      : "memory")
+  if constexpr (kCta == 1)
+    BEAM_DUAL_BODY("1");
+  else
+    BEAM_DUAL_BODY("2");
+#undef BEAM_DUAL_BODY
+}
+}  // namespace ptx
+
+template <int kStages, int kCta>
+__global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_constant__ GemmParams p) {
+  using S = DualShape<kStages, kCta>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCta == 2) ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int first = (kCta == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int items = (p.m_tiles * p.n_tiles + 1) / 2;  // work items of two tiles each
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t staging_base = smem_base + kStages * S::kStageBytes;
+  const uint32_t bar_base = staging_base + S::kStagingBytes;
+  // stage s = [A of tile 0][B of tile 0][A of tile 1][B of tile 1]
+  auto smem_a = [&](int s, int h) { return smem_base + s * S::kStageBytes + h * S::kTileBytes; };
+  auto smem_b = [&](int s, int h) { return smem_a(s, h) + S::kABytes; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      smem_gen + kStages * S::kStageBytes + S::kStagingBytes + 8 * (2 * kStages + 4));
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int num_kb = (p.k + S::kBK - 1) / S::kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), 4 * kCta);  // one arrive per epilogue warp of each CTA
+    }
+    *cta_abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&p.tm_a);
+    ptx::prefetch_tensormap(&p.tm_b);
+    ptx::prefetch_tensormap(&p.tm_c);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<kCta>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
+    ptx::tmem_relinquish<kCta>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (kCta == 2) ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      const uint64_t pol_a = ptx::l2_policy(p.hint_a);
+      const uint64_t pol_b = ptx::l2_policy(p.hint_b);
+      for (int j = 0; alive && first + j * stride < items; ++j) {
+        const int t0 = 2 * (first + j * stride);
+        int row_a[2], row_b[2];
+        for (int h = 0; h < 2; ++h) {
+          int mt, nt;
+          dual_tile_coords(p, t0 + h, mt, nt);
+          row_a[h] = mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
+          row_b[h] = nt * S::kBN + static_cast<int>(cta_rank) * S::kBRows;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {
+            alive = false;
+            break;
+          }
+          if constexpr (kCta == 1) {
+            ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+            for (int h = 0; h < 2; ++h) {
+              ptx::tma_load_2d_hint(smem_a(s, h), &p.tm_a, full_bar(s), kb * S::kBK, row_a[h], pol_a);
+              ptx::tma_load_2d_hint(smem_b(s, h), &p.tm_b, full_bar(s), kb * S::kBK, row_b[h], pol_b);
+            }
+          } else {
+            // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
+            const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
+            for (int h = 0; h < 2; ++h) {
+              ptx::tma_load_2d_pair_hint(smem_a(s, h), &p.tm_a, lead_bar, kb * S::kBK, row_a[h], pol_a);
+              ptx::tma_load_2d_pair_hint(smem_b(s, h), &p.tm_b, lead_bar, kb * S::kBK, row_b[h], pol_b);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && leader) {
+      const uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, S::kBN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
+      uint32_t stage = 0, parity = 0;
+      const uint64_t a_desc0 = ptx::umma_desc_k_sw128(smem_a(0, 0));
+      const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0, 0));
+      constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
+      constexpr uint64_t kDescTile = static_cast<uint64_t>(S::kTileBytes >> 4);
+      bool alive = true;
+      for (int j = 0; alive && first + j * stride < items; ++j) {
+        const uint32_t acc = static_cast<uint32_t>(j) & 1u;  // which pair of accumulators
+        const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
+        if (!bounded_wait(tmem_empty_bar(acc), acc_ph ^ 1u, cta_abort, p.status, kFaultMmaWaitAcc)) break;
+        ptx::tc_fence_after();
+        const uint32_t d0 = tmem_base + acc * 2u * S::kBN;
+        const uint32_t d1 = d0 + S::kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint64_t a0 = a_desc0 + stage * kDescStride;
+          const uint64_t b0 = b_desc0 + stage * kDescStride;
+          ptx::umma_f16_kblock_two_tiles<kCta>(d0, d1, a0, b0, a0 + kDescTile, b0 + kDescTile, idesc,
+                                               kb > 0 ? 1u : 0u);
+          if constexpr (kCta == 1)
+            ptx::umma_commit<1>(empty_bar(stage));
+          else
+            ptx::umma_commit_pair_both(empty_bar(stage), 0x3);
+          if (++stage == static_cast<uint32_t>(kStages)) {
+            stage = 0;
+            parity ^= 1u;
+          }
+        }
+        if (alive) {
+          if constexpr (kCta == 1)
+            ptx::umma_commit<1>(tmem_full_bar(acc));
+          else
+            ptx::umma_commit_pair_both(tmem_full_bar(acc), 0x3);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are this warp's to read
+    const uint32_t lead_empty0 = (kCta == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    uint32_t store_count = 0;
+    for (int j = 0; first + j * stride < items; ++j) {
+      const uint32_t acc = static_cast<uint32_t>(j) & 1u;
+      const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
+      if (!bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane)) break;
+      ptx::tc_fence_after();
+      const int t0 = 2 * (first + j * stride);
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        int mt, nt;
+        dual_tile_coords(p, t0 + h, mt, nt);
+        const int box_y = mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
+        const int col0 = nt * S::kBN;
+        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + (acc * 2u + static_cast<uint32_t>(h)) * S::kBN;
+#pragma unroll 1
+        for (int c = 0; c < S::kBN; c += 64) {
+          uint32_t v0[32], v1[32], out[32];
+          ptx::tmem_ld_32x32(taddr + c, v0);
+          ptx::tmem_ld_32x32(taddr + c + 32, v1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            out[q] = ptx::pack_out2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]), p.bf16);
+            out[16 + q] = ptx::pack_out2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]), p.bf16);
+          }
+          if (col0 + c < p.n && box_y < p.m) {  // warp-uniform
+            const uint32_t buf = staging_base + (quad * S::kBufsPerWarp + (store_count % S::kBufsPerWarp)) * S::kStoreBufBytes;
+            if (store_count >= static_cast<uint32_t>(S::kBufsPerWarp)) {
+              if (lane == 0) ptx::tma_store_wait_read<S::kBufsPerWarp - 1>();
+              __syncwarp();
+            }
+            const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), out[4 * jj], out[4 * jj + 1],
+                                out[4 * jj + 2], out[4 * jj + 3]);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) store_c_box(p, buf, col0 + c, box_y);
+            ++store_count;
+          }
+        }
+      }
+      // both accumulators of the item are drained: hand the pair back to the issuer
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCta == 1)
+          ptx::mbar_arrive(tmem_empty_bar(acc));
+        else
+          ptx::mbar_arrive_cluster(lead_empty0 + 8u * acc);
+      }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+  __syncwarp();
+  if (*cta_abort) abort_drain_delay();
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (kCta == 2) ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<kCta>(tmem_base, S::kTmemCols);
+  }
+}
+
+}  // namespace beam

@@ -6,9 +6,11 @@
 
 #include "gemmrc_umma.cuh"
 #include "gemm_ln_resident.cuh"
+#include "gemmrc_dual.cuh"
 #include "gemmrc_wide.cuh"
 #include "layernorm_launch.h"
 #include "splitk_launch.h"
+#include "splitk_stream.cuh"
 
 namespace beam {
 
@@ -141,52 +143,32 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
   if (items < clusters) clusters = static_cast<int>(items);
-  // One kernel per split-K call: every CTA takes exactly one (tile, slice) and all of them meet at a grid-wide
-  // barrier, so the grid must fit on the device at once.  The caller checks that before choosing this mode.
-  if (kMode == kModeSplitKFused && items > clusters) return BEAM_ERR_UNSUPPORTED;
-
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCta), 1, 1);
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[3];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kCta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (kMode == kModeLayerNorm || kMode == kModeSplitKFused) {
-    // CTAs of this grid wait for one another (the drain of LayerNorm's second pass; the barrier in front of the
-    // split-K sum): place the whole grid or none of it.
+  if (kMode == kModeLayerNorm) {
+    // CTAs of this grid wait for one another (the drain of the second pass): place the whole grid or none of it.
     attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
     attr[cfg.numAttrs].val.cooperative = 1;
     ++cfg.numAttrs;
   }
-  if (is_splitk_mode(kMode) && !(kMode == kModeSplitKFused && ctx->coop_without_pdl)) {
+  if (is_splitk_mode(kMode)) {
     // May start while the previous kernel on the stream drains; the kernel itself waits for that grid's
     // completion before its first global read or write.
     attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
     ++cfg.numAttrs;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
-  if (kMode == kModeSplitKFused && e != cudaSuccess && !ctx->coop_without_pdl &&
-      (e == cudaErrorNotSupported || e == cudaErrorInvalidValue || e == cudaErrorInvalidConfiguration)) {
-    // This driver does not take a cooperative grid as a programmatic dependent: launch it as an ordinary
-    // stream-ordered kernel from now on (griddepcontrol.wait then returns at once).
-    (void)cudaGetLastError();
-    ctx->coop_without_pdl = true;
-    --cfg.numAttrs;
-    e = cudaLaunchKernelEx(&cfg, kernel, p);
-  }
-  if (kMode == kModeSplitKFused && e == cudaErrorCooperativeLaunchTooLarge) {
-    // fewer CTAs fit at once than the device's SM count promised (a partitioned GPU): the caller runs two kernels
-    (void)cudaGetLastError();
-    return BEAM_ERR_UNSUPPORTED;
-  }
-  BEAM_CUDA_TRY(e, "cudaLaunchKernelEx(gemmrc_umma)");
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_umma)");
   return BEAM_OK;
 }
 
@@ -264,6 +246,159 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   return BEAM_OK;
 }
 
+// 128-wide tiles, two of them in flight per CTA or CTA pair (gemmrc_dual.cuh).
+template <int kStages, int kCta>
+int launch_dual_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k, int group_m,
+                         int max_ctas, const ExtraArgs& ex, cudaStream_t stream) {
+  using S = DualShape<kStages, kCta>;
+  auto kernel = gemmrc_dual_kernel<kStages, kCta>;
+  static int configured_clusters[64] = {0};
+  static std::mutex configure_mutex;
+  int resident = 0;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    resident = configured_clusters[ctx->device];
+    if (resident == 0) {
+      if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
+      BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
+                    "cudaFuncSetAttribute(smem)");
+      resident = kCta == 2 ? resident_pairs(kernel, S::kThreads, S::kSmemBytes, ctx->sm_count) : ctx->sm_count;
+      configured_clusters[ctx->device] = resident;
+    }
+  }
+  GemmParams p = {};
+  int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                          static_cast<uint64_t>(k), S::kBM, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                      S::kBRows, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n), 32,
+                      64, true);
+  if (st != BEAM_OK) return st;
+  for (int d = 0; d < ex.n_peers; ++d) {
+    st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                        static_cast<uint64_t>(n), 32, 64, true);
+    if (st != BEAM_OK) return st;
+  }
+  p.n_peers = ex.n_peers;
+  p.bf16 = ex.bf16;
+  p.c = static_cast<__half*>(C);
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ldc = n;
+  p.m_tiles = (m + S::kBM * kCta - 1) / (S::kBM * kCta);
+  p.n_tiles = (n + S::kBN - 1) / S::kBN;
+  p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 8 : 16);
+  p.slices = 1;
+  p.hint_a = (ex.l2_hints / 10) % 10;
+  p.hint_b = ex.l2_hints % 10;
+  p.hint_c = (ex.l2_hints / 100) % 10;
+  p.status = ctx->status_word;
+  const long long items = (static_cast<long long>(p.m_tiles) * p.n_tiles + 1) / 2;
+  int clusters = resident;
+  if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
+  if (items < clusters) clusters = static_cast<int>(items);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCta), 1, 1);
+  cfg.blockDim = dim3(S::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCta;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_dual)");
+  return BEAM_OK;
+}
+
+// The one-kernel split-K (splitk_stream.cuh): one CTA per (tile, slice), launched cooperatively and as a programmatic
+// dependent of whatever precedes it on the stream.  Returns BEAM_ERR_UNSUPPORTED when the grid does not fit at once.
+template <int BN, int kStages, bool kFold>
+int launch_stream_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m, int n, int k,
+                           const ExtraArgs& ex, cudaStream_t stream) {
+  using S = StreamShape<BN, kStages>;
+  auto kernel = splitk_stream_kernel<BN, kStages, kFold>;
+  static int configured[64] = {0};
+  static std::mutex configure_mutex;
+  int max_ctas = 0;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    if (configured[ctx->device] == 0) {
+      if (S::kSmemBytes > ctx->max_smem_optin) return BEAM_ERR_UNSUPPORTED;
+      BEAM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes),
+                    "cudaFuncSetAttribute(smem)");
+      int per_sm = 0;
+      BEAM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, S::kThreads, S::kSmemBytes),
+                    "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+      configured[ctx->device] = per_sm > 0 ? per_sm * ctx->sm_count : -1;
+    }
+    max_ctas = configured[ctx->device];
+  }
+  GemmParams p = {};
+  int st = encode_tmap_2d(&p.tm_a, A, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                          kFold ? S::kBM / 2 : S::kBM, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
+                      kFold ? BN / 2 : BN, S::kBK, true);
+  if (st != BEAM_OK) return st;
+  const int planes = ex.slices * (kFold ? 2 : 1);
+  st = encode_tmap_3d_f32(&p.tm_s, ex.scratch, static_cast<uint64_t>(planes), static_cast<uint64_t>(m),
+                          static_cast<uint64_t>(n), 32, 32);
+  if (st != BEAM_OK) return st;
+  p.c = static_cast<__half*>(C);
+  p.scratch = ex.scratch;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ldc = n;
+  p.m_tiles = (m + S::kBM - 1) / S::kBM;
+  p.n_tiles = (n + BN - 1) / BN;
+  p.group_m = 1;
+  p.slices = ex.slices;
+  p.flags = ex.flags;
+  p.fold = kFold ? 1 : 0;
+  p.status = ctx->status_word;
+  const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
+  // one wave that leaves the other half of every SM to the call before or after it
+  if (items > ctx->sm_count || items > max_ctas) return BEAM_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(items), 1, 1);
+  cfg.blockDim = dim3(S::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!ctx->coop_without_pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
+  if (e != cudaSuccess && cfg.numAttrs == 2 &&
+      (e == cudaErrorNotSupported || e == cudaErrorInvalidValue || e == cudaErrorInvalidConfiguration)) {
+    // This driver does not take a cooperative grid as a programmatic dependent: launch it as an ordinary
+    // stream-ordered kernel from now on (griddepcontrol.wait then returns at once).
+    (void)cudaGetLastError();
+    ctx->coop_without_pdl = true;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, p);
+  }
+  if (e == cudaErrorCooperativeLaunchTooLarge) {
+    (void)cudaGetLastError();
+    return BEAM_ERR_UNSUPPORTED;
+  }
+  BEAM_CUDA_TRY(e, "cudaLaunchKernelEx(splitk_stream)");
+  return BEAM_OK;
+}
+
 }  // namespace
 
 int default_stages(int bn, int cta) {
@@ -307,6 +442,12 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
       return tall ? launch_wide_instance<4, true>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream)
                   : launch_wide_instance<4, false>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return BEAM_ERR_UNSUPPORTED;
+  }
+  if (plan.tile_n == 128 && plan.stages == 0 && plan.tiles_in_flight != 1) {
+    // 128-wide tiles: two tiles in flight per CTA (pair), so that consecutive UMMAs never target one accumulator
+    if (plan.cta_pair == 2)
+      return launch_dual_instance<4, 2>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+    return launch_dual_instance<3, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
   }
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
@@ -437,7 +578,12 @@ size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
 // cooperative grids; BEAM_FLAG_SPLITK_TWO_KERNELS asks for the two-kernel form regardless.
 static bool splitk_one_kernel(const DeviceCtx* ctx, int m, int n, int bn, int slices, int flags) {
   if (flags & BEAM_FLAG_SPLITK_TWO_KERNELS) return false;
+  // Calls that may overlap with their neighbours stay two plain kernels: a cooperative grid that covers more than
+  // half of the device leaves no room for the next call to run beside it (measured: 19.3 against 11.9 us per call at
+  // 128 x 256 x 65536 in a train of calls).
+  if ((flags & BEAM_FLAG_INPUTS_STABLE) && !(flags & BEAM_FLAG_SPLITK_ONE_KERNEL)) return false;
   if (!ctx->cooperative_launch) return false;
+  if (bn > 128) return false;  // a 256-wide tile does not leave half of the SM free (see splitk_stream.cuh)
   const long long items = static_cast<long long>((m + 127) / 128) * ((n + bn - 1) / bn) * slices;
   return items <= ctx->sm_count;
 }
@@ -484,11 +630,10 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
     // One kernel: partials, a grid-wide barrier, then every CTA sums its share of the output (same order as the
     // reduction kernel below, so the two paths agree bit for bit).
     if (bn == 64)
-      st = launch_instance<64, 8, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
-    else if (bn == 128)
-      st = launch_instance<128, 6, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+      st = launch_stream_instance<64, 4, false>(ctx, A, B, C, m, n, k, ex, stream);
     else
-      st = launch_instance<256, 4, 1, kModeSplitKFused>(ctx, A, B, C, m, n, k, 1, 0, ex, stream);
+      st = fold ? launch_stream_instance<128, 3, true>(ctx, A, B, C, m, n, k, ex, stream)
+                : launch_stream_instance<128, 3, false>(ctx, A, B, C, m, n, k, ex, stream);
     if (st != BEAM_ERR_UNSUPPORTED) return st;
     ctx->cooperative_launch = false;  // the grid does not fit at once on this device: two kernels from now on
   }

@@ -23,9 +23,7 @@
 //   kModeGemm       fp32 -> fp16, store C.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
-//   kModeSplitKFused  the same partials, but the grid is launched cooperatively with exactly one work item per
-//                   CTA; after a grid-wide barrier every CTA sums the slices of its share of the output in the
-//                   same fixed order and stores fp16: one kernel per call, no second launch to wait for.
+//                   (Calls whose work items fit on the device at once run as one kernel instead: splitk_stream.cuh.)
 //   kModeGemmSilu   the GEMM epilogue, plus an unrelated element-wise y = x / (1 + exp(-x)) over a second tensor
 //                   that the epilogue warps work through, 1024 elements at a time, while they wait for their
 //                   next accumulator (what the reference's cute_gemm_ln.cu co-schedules on a quarter of its CTAs).
@@ -38,14 +36,12 @@
 //                   second pass is spread over all SMs and hidden under the main loops.
 #pragma once
 
-#include <cooperative_groups.h>
-
 #include "umma_common.cuh"
 
 namespace beam {
 
-enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3, kModeSplitKFused = 4 };
-__host__ __device__ constexpr bool is_splitk_mode(int mode) { return mode == kModeSplitK || mode == kModeSplitKFused; }
+enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3 };
+__host__ __device__ constexpr bool is_splitk_mode(int mode) { return mode == kModeSplitK; }
 
 struct GemmParams {
   CUtensorMap tm_a;  // A  [M, K], box 128 x 64, 128 B swizzle
@@ -356,77 +352,10 @@ __device__ __forceinline__ int ln_visit(const GemmParams& p, int& pending, uint3
 // C[r][c] = fp16( sum over planes of partial[plane][r][c] ), the planes dealt to kReduceGroups groups of
 // consecutive planes: inside a group the planes are added in ascending order, then the group sums are added
 // in ascending group order.  The association depends only on the plane count, never on timing or on how the
-// work is spread over threads, so results are bitwise reproducible, and the two callers below (the reduction
-// kernel of the two-kernel path and the tail of the one-kernel path) produce identical bits.
+// work is spread over threads, so results are bitwise reproducible, and the reduction kernel at the end of this
+// file and the tail of the one-kernel path (splitk_stream.cuh) produce identical bits.
 constexpr int kReduceGroups = 8;
 constexpr int kReduceUnitsPerPass = 16;  // float4 output groups that 128 threads (8 groups x 16) reduce together
-
-// Threads 0..127 of the CTA reduce output units [u0, u1) (a unit = 4 consecutive columns of one row; units are
-// numbered row-major).  kUnroll units per thread and kBatch planes per unit are loaded before anything is
-// added, so kUnroll * kBatch 16-byte loads are in flight per thread.  `sums` is shared memory for
-// kReduceGroups x kReduceUnitsPerPass x kUnroll float4.  Called by every thread of the CTA (uniform trip count).
-template <int kUnroll, int kBatch>
-__device__ __forceinline__ void splitk_reduce_share(const float* __restrict__ partial, __half* __restrict__ c, int m,
-                                                    int n, int planes, long long u0, long long u1, float4* sums) {
-  const int t = static_cast<int>(threadIdx.x);
-  const int g = t >> 4;        // plane group of this thread (only t < 128 work)
-  const int q = t & 15;
-  const int n4 = n >> 2;
-  const size_t plane_stride = static_cast<size_t>(m) * n;
-  const int s0 = planes * g / kReduceGroups;
-  const int s1 = planes * (g + 1) / kReduceGroups;
-  for (long long base = u0; base < u1; base += kReduceUnitsPerPass * kUnroll) {
-    if (t < 128) {
-      float4 acc[kUnroll];
-      const float* src[kUnroll];
-      bool live[kUnroll];
-#pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        const long long u = base + q + i * kReduceUnitsPerPass;
-        live[i] = u < u1;
-        const long long uu = live[i] ? u : u0;
-        src[i] = partial + (uu / n4) * n + (uu % n4) * 4;
-        acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-      for (int s = s0; s < s1; s += kBatch) {
-        float4 v[kUnroll][kBatch];
-#pragma unroll
-        for (int i = 0; i < kUnroll; ++i)
-#pragma unroll
-          for (int b = 0; b < kBatch; ++b)
-            v[i][b] = (live[i] && s + b < s1) ? __ldcg(reinterpret_cast<const float4*>(src[i] + plane_stride * (s + b)))
-                                              : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < kUnroll; ++i)
-#pragma unroll
-          for (int b = 0; b < kBatch; ++b)
-            if (s + b < s1) {
-              acc[i].x += v[i][b].x; acc[i].y += v[i][b].y; acc[i].z += v[i][b].z; acc[i].w += v[i][b].w;
-            }
-      }
-#pragma unroll
-      for (int i = 0; i < kUnroll; ++i) sums[(g * kUnroll + i) * kReduceUnitsPerPass + q] = acc[i];
-    }
-    __syncthreads();
-    if (t < kReduceUnitsPerPass * kUnroll) {
-      const int i = t >> 4;
-      const long long u = base + q + i * kReduceUnitsPerPass;
-      if (u < u1) {
-        float4 r = sums[i * kReduceUnitsPerPass + q];
-#pragma unroll
-        for (int gg = 1; gg < kReduceGroups; ++gg) {
-          const float4 w = sums[(gg * kUnroll + i) * kReduceUnitsPerPass + q];
-          r.x += w.x; r.y += w.y; r.z += w.z; r.w += w.w;
-        }
-        uint2 o;
-        o.x = ptx::pack_half2(r.x, r.y);
-        o.y = ptx::pack_half2(r.z, r.w);
-        *reinterpret_cast<uint2*>(c + (u / n4) * n + (u % n4) * 4) = o;
-      }
-    }
-    __syncthreads();
-  }
-}
 
 template <int BN, int kStages, int kCta, int kMode>
 __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
@@ -831,23 +760,6 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   // writing global memory) before the CTA goes away; then everyone meets and the allocating warp frees TMEM
   if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
   __syncwarp();
-  if constexpr (kMode == kModeSplitKFused) {
-    // Every CTA's partial is on its way to L2.  The grid was launched cooperatively with one work item per CTA, so
-    // all CTAs are resident and the grid-wide barrier below cannot wait for a CTA that has not started.  Every
-    // path reaches it, including a CTA whose bounded wait gave up (it then contributes whatever it has; the
-    // fault word tells the host that the result is invalid).  After the barrier each CTA reduces its share.
-    __threadfence();
-    cooperative_groups::this_grid().sync();
-    const int planes = p.slices * (fold ? 2 : 1);
-    const long long units = static_cast<long long>(p.m) * (p.n >> 2);  // float4 groups of the output
-    const long long u0 = units * blockIdx.x / gridDim.x;
-    const long long u1 = units * (blockIdx.x + 1) / gridDim.x;
-    float4* sums = reinterpret_cast<float4*>(smem_gen);  // the operand ring is idle by now
-    if (u1 - u0 <= kReduceUnitsPerPass)
-      splitk_reduce_share<1, 32>(p.scratch, p.c, p.m, p.n, planes, u0, u1, sums);
-    else
-      splitk_reduce_share<4, 8>(p.scratch, p.c, p.m, p.n, planes, u0, u1, sums);
-  }
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();
   __syncthreads();

@@ -61,7 +61,9 @@ typedef struct beam_gemm_cfg {
   int flags;          /* BEAM_FLAG_* bits                                                       */
   int tile_m;         /* 0 = 128 rows per CTA; 512 (with tile_n = 256, cta_pair = 2) = 512 x 256 tile per
                          CTA pair: two 256-row accumulators that multiply by the same B operand       */
-  int reserved[1];
+  int tiles_in_flight; /* tile_n = 128 with stages = 0 only: 0 or 2 = the CTA (pair) works on two neighbouring tiles at
+                         once and alternates its UMMAs between their accumulators (a UMMA of N = 128 is shorter than
+                         the wait for its predecessor's result); 1 = one tile at a time                     */
 } beam_gemm_cfg;
 
 /* Split-K only.  The caller guarantees that A and B are not outputs of the kernel that immediately precedes
@@ -77,6 +79,9 @@ typedef struct beam_gemm_cfg {
  * applies.  Both forms add the partials in the same order and agree bit for bit; this flag exists for comparison
  * and for callers that must not launch cooperative grids. */
 #define BEAM_FLAG_SPLITK_TWO_KERNELS 4
+/* Split-K only.  Run the call as one kernel wherever that form applies, including calls that carry
+ * BEAM_FLAG_INPUTS_STABLE (which run as two kernels by default). */
+#define BEAM_FLAG_SPLITK_ONE_KERNEL 8
 
 BEAM_API const char* beam_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
@@ -147,7 +152,7 @@ BEAM_API int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n);
 BEAM_API int beam_gemmrc_splitk_describe(int m, int n, int k, int tile_n, int split_k_slices, int flags, int* info);
 
 /* Generic split-K entry: cfg->tile_n (0 = default), cfg->split_k_slices (0 = heuristic) and cfg->flags
- * (BEAM_FLAG_INPUTS_STABLE, BEAM_FLAG_SPLITK_TWO_KERNELS) are honoured; cfg may be NULL.  The two registry names
+ * (BEAM_FLAG_INPUTS_STABLE, BEAM_FLAG_SPLITK_TWO_KERNELS, BEAM_FLAG_SPLITK_ONE_KERNEL) are honoured; cfg may be NULL.  The two registry names
  * below are presets. */
 BEAM_API int beam_gemmrc_splitk_fp16(const void* A, const void* B, void* C, int m, int n, int k,
                                      const beam_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,

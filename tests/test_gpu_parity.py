@@ -113,6 +113,13 @@ def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     torch.cuda.synchronize()
     assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
     assert (guard[0] == 3.0).all() and (guard[m + 1] == 3.0).all()
+    if tile_n == 128:
+        # 128-wide tiles run two tiles in flight by default (an odd tile count leaves a phantom second tile);
+        # the one-tile-at-a-time kernel must give the same bits
+        c1 = torch.full((m, n), 4.0, dtype=torch.float16, device="cuda")
+        beam.gemmrc(_dev(a), _dev(b), c1, tile_n=tile_n, cta_pair=cta_pair, tiles_in_flight=1)
+        torch.cuda.synchronize()
+        assert torch.equal(c1, c)
     _healthy(beam)
 
 
@@ -242,12 +249,13 @@ def test_config3_splitk(beam, oracle_mod, m, n, k, tile_n, slices):
     c2 = torch.zeros_like(c)
     beam.cutlass_gemmrc_splitk_spec(da, db, c2, shape_threadblock=[128, tile_n], split_k_slices=slices)
     assert torch.equal(c, c2), "split-K must be bitwise reproducible"
-    # The call runs as one cooperative kernel whenever its (tile, slice) items fit on the device at once; forced
+    # The call runs as one cooperative kernel whenever its (tile, slice) items fit on the device at once (tiles of
+    # at most 128 columns); forced
     # into the partials + reduction pair of kernels it must give the same bits (same association of the sum).
     plan = beam.splitk_describe(m, n, k, tile_n, slices)
     items = -(-m // 128) * -(-n // plan["tile_n"]) * plan["slices"]
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    assert plan["kernels_per_call"] == (1 if items <= sms else 2), plan
+    assert plan["kernels_per_call"] == (1 if items <= sms and plan["tile_n"] <= 128 else 2), plan
     c3 = torch.zeros_like(c)
     beam.cutlass_gemmrc_splitk_spec(da, db, c3, shape_threadblock=[128, tile_n], split_k_slices=slices,
                                     two_kernels=True)
