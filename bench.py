@@ -509,14 +509,22 @@ def run_ours(args):
     # ---- e2e: host buffers through the host entry, copies inside the timed region
     ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
     hc = torch.empty(M_PER_GPU, N, dtype=torch.float16).pin_memory()
+    if world > 1:
+        # Every rank holds A_local and all of B on the host; rank r uploads 1/world of B and the ranks all-gather it
+        # over NVLink, so B crosses PCIe once per step for the whole job instead of once per rank.
+        from beam.sharded import ShardedHostGemm
+        host_gemm = ShardedHostGemm(N, K)
+        e2e_call = lambda: host_gemm(ha, hb, hc)
+    else:
+        e2e_call = lambda: beam.gemmrc_host(ha, hb, hc)
     for _ in range(2):
-        beam.gemmrc_host(ha, hb, hc)
+        e2e_call()
     e2e_steps = max(3, min(args.steps, 10))
     barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        beam.gemmrc_host(ha, hb, hc)
+        e2e_call()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     barrier()
@@ -591,8 +599,12 @@ def run_ours(args):
                        "rows_per_gpu": M_PER_GPU, "kernel": "cutlass_gemmrc: 256x512 tile per CTA pair (cta_group::2, two N=256 "
                        "accumulators), 3-stage TMA ring, 8-warp TMA-store epilogue", "parallelism": "rows of A sharded x%d, B replicated, no collective" % world,
                        "l2": "A, B, C are 3 x 128 MiB per GPU, larger than the 126 MB L2; no flush between steps"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * (M_PER_GPU * K + N * K) * world,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * (M_PER_GPU * K * world + N * K),
                     "d2h_bytes_per_step": 2 * M_PER_GPU * N * world, "steps": e2e_steps, "matches_device_path": e2e_ok,
+                    "path": ("beam_gemmrc_fp16_host: A and B up in alternating row blocks, C strips back as they "
+                             "become computable" if world == 1 else
+                             "beam.sharded.ShardedHostGemm: each rank uploads its rows of A and 1/%d of B, B is "
+                             "all-gathered over NVLink (NCCL), C rows come back; per step" % world),
                     "timer": "host clock around the blocking call (copies and kernels on internal streams)"},
             "gpu_launches": args.steps,
             "clocks": clk.summary(),

@@ -29,6 +29,7 @@ __all__ = [
     "cutlass_parallel_gemmrc_silu",
     "gemmrc",
     "gemmrc_host",
+    "gemmrc_host_rows",
     "gemmrc_allgather",
     "splitk_describe",
     "release_workspaces",
@@ -97,6 +98,7 @@ def _load():
     L.beam_gemmrc_layernorm_workspace_bytes.argtypes = [i, i, i]
     L.beam_gemmrc_layernorm.argtypes = [vp, vp, vp, vp, vp, f, i, i, i, vp, sz, vp]
     L.beam_gemmrc_fp16_host.argtypes = [vp, vp, vp, i, i, i]
+    L.beam_gemmrc_fp16_host_rows.argtypes = [vp, vp, vp, i, i, i]
     L.beam_gemmrc_silu.argtypes = [vp, vp, vp, i, i, i, vp, vp, ctypes.c_longlong, vp]
     L.beam_gemmrc_fp16_allgather.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, i, i, i, ctypes.POINTER(beam_gemm_cfg), vp]
     _lib = L
@@ -363,6 +365,27 @@ def gemmrc_host(a, b, c):
     st = _load().beam_gemmrc_fp16_host(a.data_ptr(), b.data_ptr(), c.data_ptr(), int(m), int(n), int(k))
     if st != BEAM_OK:
         _raise(st, "beam_gemmrc_fp16_host")
+
+
+def gemmrc_host_rows(a, b_dev, c):
+    """a and c are CPU float16 tensors (ideally pinned), b_dev is a CUDA float16 tensor [N,K] on the current device:
+    copies a in, multiplies, copies c back; returns when c is complete.  What a rank of a row-sharded job calls
+    once B is on its GPU (see beam.sharded.ShardedHostGemm)."""
+    for name, t in (("a", a), ("c", c)):
+        if not (isinstance(t, torch.Tensor) and not t.is_cuda and t.is_contiguous() and t.dtype == torch.float16):
+            raise TypeError("%s must be a contiguous CPU float16 tensor" % name)
+    if not (isinstance(b_dev, torch.Tensor) and b_dev.is_cuda and b_dev.is_contiguous() and b_dev.dtype == torch.float16
+            and b_dev.dim() == 2):
+        raise TypeError("b_dev must be a contiguous 2-D CUDA float16 tensor")
+    m, k = a.shape
+    n, kb = b_dev.shape
+    if k != kb or tuple(c.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    with torch.cuda.device(b_dev.device):
+        torch.cuda.current_stream().synchronize()  # b_dev must be complete: the entry works on its own streams
+        st = _load().beam_gemmrc_fp16_host_rows(a.data_ptr(), b_dev.data_ptr(), c.data_ptr(), int(m), int(n), int(k))
+    if st != BEAM_OK:
+        _raise(st, "beam_gemmrc_fp16_host_rows")
 
 
 def device_status(clear=False):

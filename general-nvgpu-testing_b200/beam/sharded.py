@@ -94,3 +94,37 @@ def gemmrc_allgather(a_local: torch.Tensor, b: torch.Tensor, gathered: "Gathered
     _C.gemmrc_allgather(a_local, b, gathered.ptrs, gathered.rank, gathered.n, **knobs)
     gathered.barrier()
     return gathered.tensor
+
+
+class ShardedHostGemm:
+    """Row-sharded rc GEMM for operands that live in HOST memory on every rank: C_local = A_local @ B.T.
+
+    Sending B over PCIe once per rank would move world x |B| bytes through the host for nothing.  Here rank r
+    uploads only rows [r*N/world, (r+1)*N/world) of B, the ranks all-gather the shards over NVLink (one NCCL
+    all-gather, no host traffic), and the rank's rows of A and C then flow through beam_gemmrc_fp16_host_rows
+    (A up, C back, pipelined).  Per step and rank PCIe carries |A_local| + |B| / world up and |C_local| down.
+    """
+
+    def __init__(self, n: int, k: int, group=None, device=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.n, self.k = int(n), int(k)
+        if self.n % self.world != 0:
+            raise ValueError("N=%d must divide evenly over %d ranks" % (self.n, self.world))
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.b_dev = torch.empty((self.n, self.k), dtype=torch.float16, device=self.device)
+        self.shard = torch.empty((self.n // self.world, self.k), dtype=torch.float16, device=self.device)
+
+    def shard_rows(self) -> Tuple[int, int]:
+        """[start, stop) of the rows of B this rank uploads."""
+        per = self.n // self.world
+        return self.rank * per, (self.rank + 1) * per
+
+    def __call__(self, a_local_host: torch.Tensor, b_host: torch.Tensor, c_local_host: torch.Tensor) -> None:
+        """b_host is the whole B on the host (every rank has it); only this rank's shard of it is read."""
+        from . import _C
+        s, e = self.shard_rows()
+        self.shard.copy_(b_host[s:e], non_blocking=True)
+        dist.all_gather_into_tensor(self.b_dev, self.shard, group=self.group)
+        _C.gemmrc_host_rows(a_local_host, self.b_dev, c_local_host)

@@ -185,4 +185,8 @@ int beam_gemmrc_fp16_host(const void* A_host, const void* B_host, void* C_host, 
   return gemmrc_from_host(A_host, B_host, C_host, m, n, k);
 }
 
+int beam_gemmrc_fp16_host_rows(const void* A_host, const void* B_dev, void* C_host, int m, int n, int k) {
+  return gemmrc_rows_from_host(A_host, B_dev, C_host, m, n, k);
+}
+
 }  // extern "C"

@@ -27,6 +27,7 @@ struct ExtraArgs {
   int flags = 0;
   int fold = 0;
   int bf16 = 0;
+  int ldc = 0;  // row pitch of C in elements (0 = n): GEMM-mode kernels store C through a tensor map, so a pitch costs nothing
   const __half* ew_in = nullptr;
   __half* ew_out = nullptr;
   long long ew_count = 0;
@@ -100,8 +101,8 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.ew_out = ex.ew_out;
   p.ew_count = ex.ew_count;
   if (kMode == kModeGemm || kMode == kModeGemmSilu) {
-    st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n),
-                        32, 64, true);
+    st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                        static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, 64, true);
   } else {
     st = encode_tmap_3d_f32(&p.tm_s, ex.scratch, static_cast<uint64_t>(ex.slices) * (fold ? 2 : 1),
                             static_cast<uint64_t>(m),
@@ -200,8 +201,8 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
                       S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
-  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n), 32,
-                      64, true);
+  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                      static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, 64, true);
   if (st != BEAM_OK) return st;
   for (int d = 0; d < ex.n_peers; ++d) {
     st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
@@ -273,8 +274,8 @@ int launch_dual_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
                       S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
-  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n), static_cast<uint64_t>(n), 32,
-                      64, true);
+  st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
+                      static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, 64, true);
   if (st != BEAM_OK) return st;
   for (int d = 0; d < ex.n_peers; ++d) {
     st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
@@ -366,6 +367,20 @@ int launch_stream_instance(DeviceCtx* ctx, const void* A, const void* B, void* C
   const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
   // one wave that leaves the other half of every SM to the call before or after it
   if (items > ctx->sm_count || items > max_ctas) return BEAM_ERR_UNSUPPORTED;
+  // Read-back view: every plane's share of one CTA in one copy.  The box holds all planes (at most 256) and as many
+  // 32-byte granules as a CTA's share needs, the landing area holds and the group sums have room for.
+  if (planes > 256) return BEAM_ERR_UNSUPPORTED;
+  const long long granules = (static_cast<long long>(m) * n) >> 3;
+  long long box_g = (granules + items - 1) / items;
+  const long long fit = (S::kRingBytes - S::kSumsBytes) / 32 / planes;
+  if (box_g > fit) box_g = fit;
+  if (box_g > S::kMaxBoxGranules) box_g = S::kMaxBoxGranules;
+  if (box_g < 1) return BEAM_ERR_UNSUPPORTED;
+  st = encode_tmap_granules_f32(&p.tm_peer[0], ex.scratch, static_cast<uint64_t>(planes),
+                                static_cast<uint64_t>(granules), static_cast<uint32_t>(planes),
+                                static_cast<uint32_t>(box_g));
+  if (st != BEAM_OK) return st;
+  p.rb_granules = static_cast<int>(box_g);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(items), 1, 1);
   cfg.blockDim = dim3(S::kThreads, 1, 1);
@@ -429,6 +444,10 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
   ex.bf16 = plan.bf16;
+  if (plan.ldc != 0) {
+    if (plan.ldc < n || (plan.ldc % 8) != 0) return BEAM_ERR_INVALID_ARG;  // rows of C must stay 16-byte aligned
+    ex.ldc = plan.ldc;
+  }
   if (plan.tile_n == 512 || plan.tile_m == 512) {
     // two-accumulator tiles: 256 x 512 (tile_n = 512) or 512 x 256 (tile_m = 512, tile_n = 256)
     if (plan.cta_pair != 2) return BEAM_ERR_UNSUPPORTED;
@@ -518,9 +537,13 @@ int splitk_tile_n(int n, int tile_n) {
   return n <= 64 ? 64 : 128;
 }
 
-// Plain calls: one work item per SM (slices = SMs / tiles), but never fewer than 4 k-blocks (256 of K) per
-// slice, so that the fill of the TMA ring is amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:44-57,
-// targets the 108 SMs of an A100 and rounds to half waves.)
+// Plain calls (each call waits for the one before it), measured on B200 with chains of dependent calls over
+// HBM-cold inputs: two thirds of the SMs get a work item (128 x 256 x 65536: 16.1 us with 96 CTAs against 17.3 to
+// 18.8 with 128 to 148; fewer CTAs drain sooner and the memory system is saturated either way); folded problems
+// (M, N <= 64), which run as one kernel, do best with seven eighths (64 x 64 x 131072: 13.1 us with 128 slices
+// against 14.3 with 74).  Never fewer than 4 k-blocks (256 of K) per slice, so that the fill of the TMA ring is
+// amortised.  (The reference's model, cutlass_gemmrc_splitk.cu:44-57, targets the 108 SMs of an A100 and rounds
+// to half waves.)
 // Calls that carry BEAM_FLAG_INPUTS_STABLE overlap with their neighbours on the stream, so the grid is sized by
 // bytes instead: about 650 KB of operand traffic per CTA (820 KB when the problem runs folded), which leaves room
 // for two or three consecutive calls to stream side by side (measured optimum on B200 for 128x256x65536 and
@@ -538,9 +561,12 @@ int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
   } else {
     (void)cudaGetLastError();
   }
-  long long s = sms / (tiles > 0 ? tiles : 1);
-  if (splitk_folds(m, n, tile_n)) s = (s + 1) / 2;  // a folded slice leaves two planes: half as many slices reduce as fast
+  const bool folds = splitk_folds(m, n, tile_n);
+  long long s = (folds ? sms * 7 / 8 : sms * 2 / 3) / (tiles > 0 ? tiles : 1);
+  if (folds && s > 128) s = 128;  // a folded slice leaves two planes, and the one-kernel form reads back at most 256
   if (flags & BEAM_FLAG_INPUTS_STABLE) {
+    s = sms / (tiles > 0 ? tiles : 1);
+    if (folds) s = (s + 1) / 2;  // a folded slice leaves two planes: half as many slices reduce as fast
     // every N tile re-reads its rows of A, every M tile its rows of B (from L2 after the first reader)
     const double bytes = 2.0 * k * (static_cast<double>(m) * n_tiles + static_cast<double>(n) * m_tiles);
     const double per_cta = splitk_folds(m, n, tile_n) ? 820.0 * 1024.0 : 650.0 * 1024.0;  // folded rings hold more of K
@@ -576,14 +602,17 @@ size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
 
 // The one-kernel form needs every (tile, slice) resident at once (one CTA per SM) and a device that launches
 // cooperative grids; BEAM_FLAG_SPLITK_TWO_KERNELS asks for the two-kernel form regardless.
-static bool splitk_one_kernel(const DeviceCtx* ctx, int m, int n, int bn, int slices, int flags) {
+static bool splitk_one_kernel(const DeviceCtx* ctx, int m, int n, int bn, int slices, int flags, bool fold) {
   if (flags & BEAM_FLAG_SPLITK_TWO_KERNELS) return false;
-  // Calls that may overlap with their neighbours stay two plain kernels: a cooperative grid that covers more than
-  // half of the device leaves no room for the next call to run beside it (measured: 19.3 against 11.9 us per call at
-  // 128 x 256 x 65536 in a train of calls).
-  if ((flags & BEAM_FLAG_INPUTS_STABLE) && !(flags & BEAM_FLAG_SPLITK_ONE_KERNEL)) return false;
   if (!ctx->cooperative_launch) return false;
   if (bn > 128) return false;  // a 256-wide tile does not leave half of the SM free (see splitk_stream.cuh)
+  // Where both forms apply the faster one was chosen by measurement (B200, chains of 24 calls, HBM-cold inputs): one
+  // kernel for folded problems called plainly (13.1 against 15.0 us at 64 x 64 x 131072); two kernels otherwise
+  // (16.1 against 18.4 us at 128 x 256 x 65536; calls that overlap their neighbours: 7.7 against 8.3 us folded, 11.9
+  // against 12.4 us not).  Both forms pay about 8 us between the last UMMA and the next call's first load, a chain
+  // of device-wide round trips of about a microsecond each (stores visible, barrier or kernel boundary, read back).
+  if (!(flags & BEAM_FLAG_SPLITK_ONE_KERNEL) && (!fold || (flags & BEAM_FLAG_INPUTS_STABLE))) return false;
+  if (slices * (fold ? 2 : 1) > 256) return false;  // the read-back copy holds at most 256 planes
   const long long items = static_cast<long long>((m + 127) / 128) * ((n + bn - 1) / bn) * slices;
   return items <= ctx->sm_count;
 }
@@ -596,7 +625,7 @@ int splitk_describe(int m, int n, int k, int tile_n, int slices, int flags, int*
   const bool fold = splitk_folds(m, n, tile_n);
   const int bn = fold ? 128 : splitk_tile_n(n, tile_n);
   const int s = splitk_resolve_slices(m, n, k, tile_n, slices, flags);
-  const bool one = splitk_one_kernel(ctx, m, n, bn, s, flags);
+  const bool one = splitk_one_kernel(ctx, m, n, bn, s, flags, fold);
   info[0] = bn;
   info[1] = s;
   info[2] = fold ? 1 : 0;
@@ -626,7 +655,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   ex.slices = s;
   ex.flags = flags & BEAM_FLAG_INPUTS_STABLE;
   ex.fold = fold ? 1 : 0;
-  if (splitk_one_kernel(ctx, m, n, bn, s, flags)) {
+  if (splitk_one_kernel(ctx, m, n, bn, s, flags, fold)) {
     // One kernel: partials, a grid-wide barrier, then every CTA sums its share of the output (same order as the
     // reduction kernel below, so the two paths agree bit for bit).
     if (bn == 64)

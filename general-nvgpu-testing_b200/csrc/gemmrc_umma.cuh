@@ -49,6 +49,7 @@ struct GemmParams {
   CUtensorMap tm_c;  // C  [M, N] fp16, store box 32 rows x 64 columns, 128 B swizzle
   CUtensorMap tm_s;  // scratch [slices][M][N] fp32, store box 1 x 32 rows x 32 columns, 128 B swizzle
   CUtensorMap tm_peer[7];  // fused all-gather: this rank's row block inside each peer GPU's gathered C
+                           // (one-kernel split-K: [0] is the read-back view of the scratch, see splitk_stream.cuh)
   int n_peers;             // 0 = plain GEMM; else every C box is also stored to that many peers
   __half* c;         // fp16 output [M, ldc]
   float* scratch;    // split-K: partials [slices][M][N]; LayerNorm: fp32 panel store [M][N]
@@ -75,6 +76,7 @@ struct GemmParams {
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int lead_in;  // two-accumulator tiles: k-blocks issued half-major at the start of a tile (at least 1)
   int lead_out; // ... and at its end
+  int rb_granules;  // one-kernel split-K: 32-byte granules of every plane per read-back copy (box of tm_peer[0])
   int* status;  // device fault word
 };
 

@@ -166,4 +166,26 @@ int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint
   return BEAM_OK;
 }
 
+int encode_tmap_granules_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t granules,
+                             uint32_t box_planes, uint32_t box_granules) {
+  const TmapKey key = {base, granules, planes, 0, 0, box_granules, box_planes, 0x2000u};
+  if (tmap_lookup(key, out)) return BEAM_OK;
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return BEAM_ERR_TENSORMAP;
+  const cuuint64_t gdim[3] = {8, granules, planes};
+  const cuuint64_t gstride[2] = {32, granules * 32};
+  const cuuint32_t box[3] = {8, box_granules, box_planes};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), gdim, gstride, box, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled (granules) failed with CUresult %d",
+                  static_cast<int>(r));
+    return BEAM_ERR_TENSORMAP;
+  }
+  tmap_remember(key, out);
+  return BEAM_OK;
+}
+
 }  // namespace beam

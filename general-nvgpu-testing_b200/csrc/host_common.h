@@ -38,6 +38,11 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
 int encode_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                        uint32_t box_rows, uint32_t box_cols);
 
+// The same dense fp32 tensor [planes][rows * cols] seen as [planes][granules][8 floats] (32-byte granules, no
+// swizzle), box = box_planes x box_granules x 8: the read-back view of the one-kernel split-K.
+int encode_tmap_granules_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t granules,
+                             uint32_t box_planes, uint32_t box_granules);
+
 // Records a CUDA runtime failure for beam_last_cuda_error() (thread-local text).
 void note_cuda_error(cudaError_t e, const char* where);
 const char* last_cuda_error_text();

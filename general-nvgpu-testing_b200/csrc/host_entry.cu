@@ -1,7 +1,13 @@
-// Host-buffer entry point: the caller's A, B and C live in host memory.  B is copied whole; A is
-// copied in row blocks, each block's GEMM is launched as soon as its rows have landed, and each
-// block of C starts its way back as soon as it is computed, so that the two PCIe directions and
-// the tensor cores work at the same time.  Staging buffers are per device, grow-only.
+// Host-buffer entry points: the caller's A and C (and, in the first form, B) live in host memory.
+//
+// PCIe is the whole cost here (at 8192^3 the kernel needs 0.7 ms, the copies 5 to 6), and the link carries less in
+// each direction when both are busy than when one is (measured on B200 hosts: 55 GB/s one way, about 79 GB/s for
+// both together).  So the schedule is built to keep both directions busy for as long as possible: A and B go up in
+// row blocks, alternating, and after every arrival the strip of C that has just become computable (the new rows of
+// A against every row of B that has landed, or the new rows of B against every row of A) is multiplied and starts
+// its way back at once.  The computable area grows like a square, C begins to flow after the second block instead
+// of after all of B, and only the last strip's copy is left when the uploads end.  Copies in, kernels and copies
+// out run on three streams ordered by events; staging buffers are per device and grow-only.
 #include "host_entry.h"
 
 #include <mutex>
@@ -13,19 +19,19 @@ namespace beam {
 namespace {
 
 struct HostPath {
+  std::mutex mutex;  // one call at a time per device (the staging buffers are shared)
   void* dA = nullptr;
   void* dB = nullptr;
   void* dC = nullptr;
   size_t capA = 0, capB = 0, capC = 0;
   cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
-  static constexpr int kMaxBlocks = 64;
-  cudaEvent_t landed[kMaxBlocks] = {};
-  cudaEvent_t computed[kMaxBlocks] = {};
+  static constexpr int kMaxSteps = 64;
+  cudaEvent_t landed[kMaxSteps] = {};
+  cudaEvent_t computed[kMaxSteps] = {};
   bool ready = false;
 };
 
 HostPath g_host[64];
-std::mutex g_host_mutex;
 
 int grow(void** p, size_t* cap, size_t need) {
   if (*cap >= need) return BEAM_OK;
@@ -37,61 +43,109 @@ int grow(void** p, size_t* cap, size_t need) {
   return BEAM_OK;
 }
 
-}  // namespace
+// Rows per block: about an eighth of the dimension, a multiple of 256 (a pair tile), so that at most kMaxSteps / 2
+// blocks cover it.
+int block_rows(int dim) {
+  int rows = ((dim + 7) / 8 + 255) / 256 * 256;
+  while ((dim + rows - 1) / rows > HostPath::kMaxSteps / 2) rows *= 2;
+  return rows;
+}
 
-int gemmrc_from_host(const void* A_host, const void* B_host, void* C_host, int m, int n, int k) {
-  if (!A_host || !B_host || !C_host || m <= 0 || n <= 0 || k <= 0) return BEAM_ERR_INVALID_ARG;
+// The body of a call; any failure leaves work in flight on the internal streams, which the caller drains.
+int run_pipeline(HostPath& h, const void* A_host, const void* B_host, const void* B_dev, void* C_host, int m, int n,
+                 int k) {
+  const size_t row_a = static_cast<size_t>(k) * 2, row_c = static_cast<size_t>(n) * 2;
+  int st;
+  if ((st = grow(&h.dA, &h.capA, static_cast<size_t>(m) * row_a)) != BEAM_OK) return st;
+  if ((st = grow(&h.dC, &h.capC, static_cast<size_t>(m) * row_c)) != BEAM_OK) return st;
+  const char* devB = static_cast<const char*>(B_dev);
+  if (!devB) {
+    if ((st = grow(&h.dB, &h.capB, static_cast<size_t>(n) * row_a)) != BEAM_OK) return st;
+    devB = static_cast<const char*>(h.dB);
+  }
+  const int blk_a = block_rows(m), blk_b = block_rows(n);
+  int a_done = 0, b_done = B_dev ? n : 0;  // rows of A / of B whose upload has been queued
+  int step = 0;
+  while (a_done < m || b_done < n) {
+    // B goes first and the two alternate while both have rows left (the computable area stays close to a square).
+    const bool take_b = b_done < n && (a_done >= m || b_done <= a_done);
+    const int r0 = take_b ? b_done : a_done;
+    const int rows = take_b ? (n - r0 < blk_b ? n - r0 : blk_b) : (m - r0 < blk_a ? m - r0 : blk_a);
+    const char* src = static_cast<const char*>(take_b ? B_host : A_host) + static_cast<size_t>(r0) * row_a;
+    char* dst = (take_b ? static_cast<char*>(h.dB) : static_cast<char*>(h.dA)) + static_cast<size_t>(r0) * row_a;
+    BEAM_CUDA_TRY(cudaMemcpyAsync(dst, src, static_cast<size_t>(rows) * row_a, cudaMemcpyHostToDevice, h.s_in), "H2D");
+    BEAM_CUDA_TRY(cudaEventRecord(h.landed[step], h.s_in), "event record");
+    // the strip of C that became computable: new rows x landed columns, or landed rows x new columns
+    const int c_r0 = take_b ? 0 : r0, c_rows = take_b ? a_done : rows;
+    const int c_c0 = take_b ? r0 : 0, c_cols = take_b ? rows : b_done;
+    if (take_b)
+      b_done += rows;
+    else
+      a_done += rows;
+    if (c_rows > 0 && c_cols > 0) {
+      BEAM_CUDA_TRY(cudaStreamWaitEvent(h.s_mm, h.landed[step], 0), "stream wait");
+      GemmPlan plan;
+      plan.ldc = n;
+      // the headline tile (256 x 512 per CTA pair) once a strip has a few waves of them
+      if (static_cast<long long>((c_rows + 255) / 256) * ((c_cols + 511) / 512) >= 2 * 74) plan.tile_n = 512;
+      char* devC = static_cast<char*>(h.dC) + static_cast<size_t>(c_r0) * row_c + static_cast<size_t>(c_c0) * 2;
+      st = launch_gemmrc(static_cast<const char*>(h.dA) + static_cast<size_t>(c_r0) * row_a,
+                         devB + static_cast<size_t>(c_c0) * row_a, devC, c_rows, c_cols, k, plan, h.s_mm);
+      if (st != BEAM_OK) return st;
+      BEAM_CUDA_TRY(cudaEventRecord(h.computed[step], h.s_mm), "event record");
+      BEAM_CUDA_TRY(cudaStreamWaitEvent(h.s_out, h.computed[step], 0), "stream wait");
+      char* hostC = static_cast<char*>(C_host) + static_cast<size_t>(c_r0) * row_c + static_cast<size_t>(c_c0) * 2;
+      BEAM_CUDA_TRY(cudaMemcpy2DAsync(hostC, row_c, devC, row_c, static_cast<size_t>(c_cols) * 2,
+                                      static_cast<size_t>(c_rows), cudaMemcpyDeviceToHost, h.s_out),
+                    "D2H C");
+    }
+    ++step;
+  }
+  return BEAM_OK;
+}
+
+int from_host(const void* A_host, const void* B_host, const void* B_dev, void* C_host, int m, int n, int k) {
+  if (!A_host || !(B_host || B_dev) || !C_host || m <= 0 || n <= 0 || k <= 0) return BEAM_ERR_INVALID_ARG;
   if ((k % 8) != 0 || (n % 8) != 0) return BEAM_ERR_ALIGNMENT;
+  if (B_dev && !aligned16(B_dev)) return BEAM_ERR_ALIGNMENT;
   int st = BEAM_OK;
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
-  std::lock_guard<std::mutex> lock(g_host_mutex);
   HostPath& h = g_host[ctx->device];
+  std::lock_guard<std::mutex> lock(h.mutex);
   if (!h.ready) {
     BEAM_CUDA_TRY(cudaStreamCreateWithFlags(&h.s_in, cudaStreamNonBlocking), "stream");
     BEAM_CUDA_TRY(cudaStreamCreateWithFlags(&h.s_mm, cudaStreamNonBlocking), "stream");
     BEAM_CUDA_TRY(cudaStreamCreateWithFlags(&h.s_out, cudaStreamNonBlocking), "stream");
-    for (int i = 0; i < HostPath::kMaxBlocks; ++i) {
+    for (int i = 0; i < HostPath::kMaxSteps; ++i) {
       BEAM_CUDA_TRY(cudaEventCreateWithFlags(&h.landed[i], cudaEventDisableTiming), "event");
       BEAM_CUDA_TRY(cudaEventCreateWithFlags(&h.computed[i], cudaEventDisableTiming), "event");
     }
     h.ready = true;
   }
-  const size_t bytesA = static_cast<size_t>(m) * k * 2, bytesB = static_cast<size_t>(n) * k * 2,
-               bytesC = static_cast<size_t>(m) * n * 2;
-  if ((st = grow(&h.dA, &h.capA, bytesA)) != BEAM_OK) return st;
-  if ((st = grow(&h.dB, &h.capB, bytesB)) != BEAM_OK) return st;
-  if ((st = grow(&h.dC, &h.capC, bytesC)) != BEAM_OK) return st;
-
-  // Row blocks of A: multiples of 256 rows (a pair tile), about 16 blocks, at most kMaxBlocks.
-  int rows_per_block = ((m + 15) / 16 + 255) / 256 * 256;
-  while ((m + rows_per_block - 1) / rows_per_block > HostPath::kMaxBlocks) rows_per_block *= 2;
-  const int blocks = (m + rows_per_block - 1) / rows_per_block;
-
-  BEAM_CUDA_TRY(cudaMemcpyAsync(h.dB, B_host, bytesB, cudaMemcpyHostToDevice, h.s_in), "H2D B");
-  GemmPlan plan;
-  for (int b = 0; b < blocks; ++b) {
-    const int r0 = b * rows_per_block;
-    const int rows = (m - r0 < rows_per_block) ? (m - r0) : rows_per_block;
-    const char* srcA = static_cast<const char*>(A_host) + static_cast<size_t>(r0) * k * 2;
-    char* dstA = static_cast<char*>(h.dA) + static_cast<size_t>(r0) * k * 2;
-    char* devC = static_cast<char*>(h.dC) + static_cast<size_t>(r0) * n * 2;
-    char* dstC = static_cast<char*>(C_host) + static_cast<size_t>(r0) * n * 2;
-    BEAM_CUDA_TRY(cudaMemcpyAsync(dstA, srcA, static_cast<size_t>(rows) * k * 2, cudaMemcpyHostToDevice, h.s_in),
-                  "H2D A");
-    BEAM_CUDA_TRY(cudaEventRecord(h.landed[b], h.s_in), "event record");
-    BEAM_CUDA_TRY(cudaStreamWaitEvent(h.s_mm, h.landed[b], 0), "stream wait");
-    st = launch_gemmrc(dstA, h.dB, devC, rows, n, k, plan, h.s_mm);
-    if (st != BEAM_OK) return st;
-    BEAM_CUDA_TRY(cudaEventRecord(h.computed[b], h.s_mm), "event record");
-    BEAM_CUDA_TRY(cudaStreamWaitEvent(h.s_out, h.computed[b], 0), "stream wait");
-    BEAM_CUDA_TRY(cudaMemcpyAsync(dstC, devC, static_cast<size_t>(rows) * n * 2, cudaMemcpyDeviceToHost, h.s_out),
-                  "D2H C");
-  }
-  BEAM_CUDA_TRY(cudaStreamSynchronize(h.s_out), "sync");
-  BEAM_CUDA_TRY(cudaStreamSynchronize(h.s_mm), "sync");
-  BEAM_CUDA_TRY(cudaStreamSynchronize(h.s_in), "sync");
+  st = run_pipeline(h, A_host, B_host, B_dev, C_host, m, n, k);
+  // Success or not, nothing of this call may still be in flight when it returns: the next call reuses the staging
+  // buffers and events, and the copies out target the caller's memory.
+  const cudaError_t e_out = cudaStreamSynchronize(h.s_out);
+  const cudaError_t e_mm = cudaStreamSynchronize(h.s_mm);
+  const cudaError_t e_in = cudaStreamSynchronize(h.s_in);
+  if (st != BEAM_OK) return st;
+  BEAM_CUDA_TRY(e_out, "sync");
+  BEAM_CUDA_TRY(e_mm, "sync");
+  BEAM_CUDA_TRY(e_in, "sync");
   return BEAM_OK;
+}
+
+}  // namespace
+
+int gemmrc_from_host(const void* A_host, const void* B_host, void* C_host, int m, int n, int k) {
+  if (!B_host) return BEAM_ERR_INVALID_ARG;
+  return from_host(A_host, B_host, nullptr, C_host, m, n, k);
+}
+
+int gemmrc_rows_from_host(const void* A_host, const void* B_dev, void* C_host, int m, int n, int k) {
+  if (!B_dev) return BEAM_ERR_INVALID_ARG;
+  return from_host(A_host, nullptr, B_dev, C_host, m, n, k);
 }
 
 }  // namespace beam

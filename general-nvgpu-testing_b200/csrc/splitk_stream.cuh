@@ -14,8 +14,8 @@
 //     launch) become resident beside this call's and finish their whole set-up while this call is still running;
 //   * the accumulator is pulled out of TMEM with all loads in flight at once and staged in the (by then idle)
 //     operand ring, from where TMA stores move it to the workspace;
-//   * after the barrier the partials come back as bulk copies into shared memory, one per plane, all in flight at
-//     once, and are summed from there.
+//   * after the barrier the partials come back as ONE tiled TMA copy per CTA (all planes of the CTA's share of
+//     the output at once) and are summed from shared memory.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -34,6 +34,8 @@ struct StreamShape {
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
   static constexpr int kBarBytes = 256;
+  static constexpr int kSumsBytes = 32 * 1024;      // group sums of the final reduction: 8 groups x 256 float4
+  static constexpr int kMaxBoxGranules = 128;       // 32-byte granules of one plane per read-back copy (256 units)
   static constexpr int kSmemBytes = kRingBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kThreads = 192;
   // The drained accumulator (128 rows x BN fp32) is staged in the ring before it leaves through TMA.
@@ -94,6 +96,7 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
     ptx::prefetch_tensormap(&p.tm_s);
+    ptx::prefetch_tensormap(&p.tm_peer[0]);
     // The next kernel on the stream may become resident now; it blocks in its own griddepcontrol.wait.
     ptx::grid_launch_dependents();
   }
@@ -221,65 +224,61 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
   __threadfence();
   cooperative_groups::this_grid().sync();
   {
+    // The workspace is read back through a second tensor map that sees it as [planes][M * N / 8][8 floats]
+    // ("granules" of 32 bytes, numbered row-major over the output): ONE tiled copy brings a run of granules of
+    // EVERY plane into shared memory (plane s at offset s * rb_granules * 32).  Issuing a copy per plane from one
+    // thread instead costs about 60 ns per copy, 4 us for 64 planes.  This CTA's share is granules [g0, g1).
     const int planes = p.slices * (kFold ? 2 : 1);
-    const long long units = static_cast<long long>(p.m) * (p.n >> 2);  // float4 groups of the output, row-major
-    const long long u0 = units * blockIdx.x / gridDim.x;
-    const long long u1 = units * (blockIdx.x + 1) / gridDim.x;
-    const size_t plane_stride = static_cast<size_t>(p.m) * p.n;
-    // A round brings `span` units of every plane into the ring (plane s at offset s * span * 16); the tail of the
-    // ring holds the group sums.  The host only chooses this kernel when at least one unit per plane fits.
-    constexpr int kSumsBytes = kReduceGroups * kReduceUnitsPerPass * 16;
-    long long span_max = (S::kRingBytes - kSumsBytes) / 16 / planes;
-    if (span_max > 4096) span_max = 4096;
-    if (span_max < 1) span_max = 1;
+    const long long granules = (static_cast<long long>(p.m) * p.n) >> 3;
+    const long long g0 = granules * blockIdx.x / gridDim.x;
+    const long long g1 = granules * (blockIdx.x + 1) / gridDim.x;
+    const int box_g = p.rb_granules;                       // granules per copy (what the tensor map's box holds)
+    const uint32_t plane_bytes = static_cast<uint32_t>(box_g) * 32u;
+    const uint32_t box_bytes = plane_bytes * static_cast<uint32_t>(planes);
     const int t = static_cast<int>(threadIdx.x);
     const int g = t >> 4, q = t & 15;
     const int s0 = planes * g / kReduceGroups, s1 = planes * (g + 1) / kReduceGroups;
     const int n4 = p.n >> 2;
-    float4* sums = reinterpret_cast<float4*>(smem_gen + S::kRingBytes - kSumsBytes);
+    // group sums: [kReduceGroups][2 * box_g units] float4 at the tail of the ring (the host keeps box_g <= 128)
+    float4* sums = reinterpret_cast<float4*>(smem_gen + S::kRingBytes - S::kSumsBytes);
     uint32_t round = 0;
-    for (long long base = u0; base < u1; base += span_max, ++round) {
-      const long long span = (u1 - base < span_max) ? (u1 - base) : span_max;
-      const uint32_t seg = static_cast<uint32_t>(span) * 16u;
+    for (long long gc = g0; gc < g1; gc += box_g, ++round) {
+      const int ng = static_cast<int>((g1 - gc < box_g) ? (g1 - gc) : box_g);  // granules of this round that are ours
       if (threadIdx.x == 0) {
-        ptx::mbar_arrive_expect_tx(reduce_bar, seg * static_cast<uint32_t>(planes));
-        const float* src = p.scratch + (base / n4) * p.n + (base % n4) * 4;
-        for (int s = 0; s < planes; ++s)
-          ptx::bulk_load(smem_base + static_cast<uint32_t>(s) * seg, src + plane_stride * s, seg, reduce_bar);
+        ptx::mbar_arrive_expect_tx(reduce_bar, box_bytes);
+        ptx::tma_load_3d(smem_base, &p.tm_peer[0], reduce_bar, 0, static_cast<int>(gc), 0);
       }
       // every thread waits on the barrier itself (whoever sees the phase complete sees the copied bytes); the
       // verdict is made uniform so that nobody is left behind at a CTA barrier
       const int landed = bounded_wait(reduce_bar, round & 1u, cta_abort, p.status, kFaultReduceWait) ? 1 : 0;
       if (!__syncthreads_and(landed)) break;
-      for (long long ub = 0; ub < span; ub += kReduceUnitsPerPass) {
-        if (t < 128) {
+      const int nu = 2 * ng;  // float4 units of this round
+      if (t < 128) {
+        for (int u = q; u < nu; u += kReduceUnitsPerPass) {
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (ub + q < span) {
-            const uint32_t addr = smem_base + static_cast<uint32_t>(ub + q) * 16u;
-            for (int s = s0; s < s1; ++s) {
-              const float4 v = ptx::ld_shared_f4(addr + static_cast<uint32_t>(s) * seg);
-              acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
+          const uint32_t addr = smem_base + static_cast<uint32_t>(u) * 16u;
+          for (int sp = s0; sp < s1; ++sp) {
+            const float4 v = ptx::ld_shared_f4(addr + static_cast<uint32_t>(sp) * plane_bytes);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
           }
-          sums[g * kReduceUnitsPerPass + q] = acc;
+          sums[g * (2 * box_g) + u] = acc;
         }
-        __syncthreads();
-        if (t < kReduceUnitsPerPass && ub + t < span) {
-          float4 r = sums[t];
-#pragma unroll
-          for (int gg = 1; gg < kReduceGroups; ++gg) {
-            const float4 w = sums[gg * kReduceUnitsPerPass + t];
-            r.x += w.x; r.y += w.y; r.z += w.z; r.w += w.w;
-          }
-          const long long u = base + ub + t;
-          uint2 o;
-          o.x = ptx::pack_half2(r.x, r.y);
-          o.y = ptx::pack_half2(r.z, r.w);
-          *reinterpret_cast<uint2*>(p.c + (u / n4) * p.n + (u % n4) * 4) = o;
-        }
-        __syncthreads();
       }
-      // the next round's copies overwrite what this round's loads read: generic reads before async writes
+      __syncthreads();
+      for (int u = t; u < nu; u += S::kThreads) {
+        float4 r = sums[u];
+#pragma unroll
+        for (int gg = 1; gg < kReduceGroups; ++gg) {
+          const float4 w = sums[gg * (2 * box_g) + u];
+          r.x += w.x; r.y += w.y; r.z += w.z; r.w += w.w;
+        }
+        const long long unit = 2 * gc + u;
+        uint2 o;
+        o.x = ptx::pack_half2(r.x, r.y);
+        o.y = ptx::pack_half2(r.z, r.w);
+        *reinterpret_cast<uint2*>(p.c + (unit / n4) * p.n + (unit % n4) * 4) = o;
+      }
+      // the next round's copy overwrites what this round's loads read: generic reads before async writes
       ptx::fence_proxy_async_smem();
       __syncthreads();
     }

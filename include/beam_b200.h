@@ -223,10 +223,17 @@ BEAM_API int beam_gemmrc_silu(const void* A, const void* B, void* C, int m, int 
 
 /* ---- host-buffer convenience (what a caller with pageable or pinned HOST arrays uses) ---------- */
 
-/* A, B, C are HOST pointers. Copies A and B to the device in row blocks, runs beam_cutlass_gemmrc on
- * each block as it lands and copies C back, overlapping the three on separate streams; blocks until
- * C is complete.  Device staging buffers are allocated on the first call and reused while they fit. */
+/* A, B, C are HOST pointers (pinned memory for full PCIe speed).  A and B go to the device in alternating row
+ * blocks; after every arrival the strip of C that has become computable is multiplied and copied back, so both
+ * directions of the link are busy from the second block on; blocks until C is complete.  Device staging buffers
+ * are allocated on the first call on a device and reused while they fit; calls on one device run one at a time. */
 BEAM_API int beam_gemmrc_fp16_host(const void* A_host, const void* B_host, void* C_host, int m, int n, int k);
+
+/* The same with B already resident on the device (B_dev: device pointer, [N,K] fp16, 16-byte aligned): only A goes
+ * up and only C comes back.  For the ranks of a row-sharded job (no counterpart in the reference, which is
+ * single-GPU): each rank uploads 1/world of B, the ranks all-gather B over NVLink, and every step then moves just
+ * the rank's own rows of A and C over PCIe. */
+BEAM_API int beam_gemmrc_fp16_host_rows(const void* A_host, const void* B_dev, void* C_host, int m, int n, int k);
 
 #ifdef __cplusplus
 }

@@ -249,20 +249,24 @@ def test_config3_splitk(beam, oracle_mod, m, n, k, tile_n, slices):
     c2 = torch.zeros_like(c)
     beam.cutlass_gemmrc_splitk_spec(da, db, c2, shape_threadblock=[128, tile_n], split_k_slices=slices)
     assert torch.equal(c, c2), "split-K must be bitwise reproducible"
-    # The call runs as one cooperative kernel whenever its (tile, slice) items fit on the device at once (tiles of
-    # at most 128 columns); forced
-    # into the partials + reduction pair of kernels it must give the same bits (same association of the sum).
+    # A call can run as one cooperative kernel when its (tile, slice) items fit on the device at once (tiles of at
+    # most 128 columns, at most 256 partial planes); the library picks that form for folded problems and two kernels
+    # otherwise.  Forced either way, the bits must be those of the default: the sum is associated identically.
     plan = beam.splitk_describe(m, n, k, tile_n, slices)
     items = -(-m // 128) * -(-n // plan["tile_n"]) * plan["slices"]
+    planes = plan["slices"] * (2 if plan["folded"] else 1)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    assert plan["kernels_per_call"] == (1 if items <= sms and plan["tile_n"] <= 128 else 2), plan
-    c3 = torch.zeros_like(c)
-    beam.cutlass_gemmrc_splitk_spec(da, db, c3, shape_threadblock=[128, tile_n], split_k_slices=slices,
-                                    two_kernels=True)
-    torch.cuda.synchronize()
-    _healthy(beam)
+    can_fuse = items <= sms and plan["tile_n"] <= 128 and planes <= 256
+    assert plan["kernels_per_call"] == (1 if can_fuse and plan["folded"] else 2), plan
     assert beam.splitk_describe(m, n, k, tile_n, slices, two_kernels=True)["kernels_per_call"] == 2
-    assert torch.equal(c, c3), "one-kernel and two-kernel split-K must agree bit for bit"
+    assert beam.splitk_describe(m, n, k, tile_n, slices, two_kernels=False)["kernels_per_call"] == (1 if can_fuse else 2)
+    for forced in (True, False):
+        c3 = torch.zeros_like(c)
+        beam.cutlass_gemmrc_splitk_spec(da, db, c3, shape_threadblock=[128, tile_n], split_k_slices=slices,
+                                        two_kernels=forced)
+        torch.cuda.synchronize()
+        _healthy(beam)
+        assert torch.equal(c, c3), "one-kernel and two-kernel split-K must agree bit for bit (two_kernels=%s)" % forced
 
 
 @pytest.mark.parametrize("m,n,k,tile_n,slices", [(128, 256, 16384, 128, 32), (64, 64, 32768, 64, 0),
@@ -277,10 +281,13 @@ def test_splitk_exact_on_integer_inputs(beam, oracle_mod, m, n, k, tile_n, slice
     want = oracle_mod.gemmrc_splitk(a, b, s)
     assert np.array_equal(want, oracle_mod.gemmrc(a, b))
     c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
-    beam.cutlass_gemmrc_splitk_spec(_dev(a), _dev(b), c, shape_threadblock=[128, tile_n], split_k_slices=slices)
-    torch.cuda.synchronize()
-    _healthy(beam)
-    assert np.array_equal(c.cpu().numpy(), want)
+    for forced in (None, True, False):
+        c.zero_()
+        beam.cutlass_gemmrc_splitk_spec(_dev(a), _dev(b), c, shape_threadblock=[128, tile_n], split_k_slices=slices,
+                                        two_kernels=forced)
+        torch.cuda.synchronize()
+        _healthy(beam)
+        assert np.array_equal(c.cpu().numpy(), want), forced
 
 
 def test_splitk_default_entry(beam, oracle_mod):
@@ -435,6 +442,26 @@ def test_host_buffer_entry(beam, oracle_mod):
     assert torch.equal(pc, c)
 
 
+@pytest.mark.parametrize("m,n,k", [(1000, 520, 264), (2304, 1800, 512), (300, 4104, 128), (4096, 264, 1024)])
+def test_host_buffer_entry_strips(beam, oracle_mod, m, n, k):
+    """The host entry multiplies strip by strip as row blocks of A and B arrive (several blocks per dimension here,
+    ragged last blocks included) and writes each strip into C with a row pitch: every element must be there, and the
+    form with B already on the device must give the same bits."""
+    a, b = _inputs(m, n, k, 0.1, m + n + k)
+    want = oracle_mod.gemmrc(a, b)
+    pa, pb = torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()
+    pc = torch.full((m, n), 9.0, dtype=torch.float16).pin_memory()
+    beam.gemmrc_host(pa, pb, pc)
+    assert oracle_mod.floored_max_rel(pc.numpy(), want) <= oracle_mod.REL_TOL
+    dc = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc(pa.cuda(), pb.cuda(), dc)
+    assert torch.equal(dc.cpu(), pc), "host-buffer path and device path must agree bit for bit"
+    pc2 = torch.full((m, n), 7.0, dtype=torch.float16).pin_memory()
+    beam.gemmrc_host_rows(pa, pb.cuda(), pc2)
+    assert torch.equal(pc2, pc)
+    _healthy(beam)
+
+
 def test_reference_kernels_agree_with_oracle_and_ours(beam, oracle_mod):
     """Second parity witness: the reference's own kernels (built unmodified for sm_100a by
     baseline/build_reference.py; skipped when that build is absent) against the CPU oracle and against the new
@@ -472,6 +499,32 @@ def test_overlapped_splitk_calls(beam, oracle_mod):
     for rep in range(3):
         for da, db, _, c in cases:
             beam.cutlass_gemmrc_splitk(da, db, c, split_k_slices=0, inputs_stable=True)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    for _, _, want, c in cases:
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+
+
+def test_one_kernel_splitk_overlapped_and_on_two_streams(beam, oracle_mod):
+    """The one-kernel split-K is a cooperative grid launched as a programmatic dependent.  Trains of such calls that
+    may overlap (BEAM_FLAG_INPUTS_STABLE), and two trains on two streams at once (each with its own scratch: the
+    binding keeps one per stream), must still give every call its own result."""
+    cases = []
+    for i in range(4):
+        a, b = _inputs(64, 64, 32768, "uniform", 700 + i)
+        cases.append((_dev(a), _dev(b), oracle_mod.gemmrc(a, b), torch.zeros(64, 64, dtype=torch.float16, device="cuda")))
+    for da, db, _, c in cases * 3:
+        beam.cutlass_gemmrc_splitk(da, db, c, inputs_stable=True, two_kernels=False)
+    torch.cuda.synchronize()
+    _healthy(beam)
+    for _, _, want, c in cases:
+        assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+        c.zero_()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for rep in range(5):
+        for idx, (da, db, _, c) in enumerate(cases):
+            with torch.cuda.stream(streams[idx % 2]):
+                beam.cutlass_gemmrc_splitk(da, db, c, two_kernels=False)
     torch.cuda.synchronize()
     _healthy(beam)
     for _, _, want, c in cases:

@@ -72,6 +72,20 @@ def _worker(rank, world, port, out_dir):
         beam.cutlass_parallel_gemmrc_lnr(torch.cat(xs), w, full, gamma, beta, 1e-5)
         torch.cuda.synchronize()
         assert torch.equal(got, full), "sharded LayerNorm, rank %d" % rank
+        # Host-resident operands: each rank uploads 1/world of B, the ranks all-gather it over NVLink, and only the
+        # rank's own rows of A and C cross PCIe.
+        from beam.sharded import ShardedHostGemm
+        m_local, n, k = 1280, 1024, 512
+        gb = torch.Generator().manual_seed(31)
+        b_host = (torch.randn(n, k, generator=gb) * 0.1).half().pin_memory()
+        a_host = (torch.randn(m_local, k, generator=torch.Generator().manual_seed(40 + rank)) * 0.1).half().pin_memory()
+        c_host = torch.zeros(m_local, n, dtype=torch.float16).pin_memory()
+        ShardedHostGemm(n, k)(a_host, b_host, c_host)
+        c_dev = torch.empty(m_local, n, dtype=torch.float16, device="cuda")
+        beam.cutlass_gemmrc(a_host.cuda(), b_host.cuda(), c_dev)
+        torch.cuda.synchronize()
+        assert torch.equal(c_dev.cpu(), c_host), "sharded host GEMM, rank %d" % rank
+        assert oracle.floored_max_rel(c_host.numpy(), oracle.gemmrc(a_host.numpy(), b_host.numpy())) <= oracle.REL_TOL
         st, word = beam.device_status()
         assert (st, word) == (0, 0)
         open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
