@@ -601,8 +601,10 @@ int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested, int fl
 
 size_t splitk_workspace_bytes(int m, int n, int k, int tile_n, int slices) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  // sized for the plain heuristic, which never picks fewer slices than the overlapped one
-  const int s = splitk_resolve_slices(m, n, k, tile_n, slices, 0);
+  // sized for whichever of the two heuristics (plain calls, calls that may overlap) picks more slices
+  const int s_plain = splitk_resolve_slices(m, n, k, tile_n, slices, 0);
+  const int s_over = splitk_resolve_slices(m, n, k, tile_n, slices, BEAM_FLAG_INPUTS_STABLE);
+  const int s = s_plain > s_over ? s_plain : s_over;
   const size_t planes = static_cast<size_t>(s) * (splitk_folds(m, n, tile_n) ? 2 : 1);
   return planes * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
 }
