@@ -73,14 +73,11 @@ int beam_gemmrc_fp16_allgather(const void* A_local, const void* B, void* const* 
     if (cfg->cta_pair) plan.cta_pair = cfg->cta_pair;
     plan.stages = cfg->stages;
     plan.group_m = cfg->group_m;
-    plan.gather_box_cols = cfg->gather_box_cols;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
     if (plan.stages < 0 || plan.group_m < 0) return BEAM_ERR_INVALID_ARG;
-    if (plan.gather_box_cols != 0 && plan.gather_box_cols != 64 && plan.gather_box_cols != 128) return BEAM_ERR_INVALID_ARG;
-  }
-  if (!cfg || cfg->tile_n == 0) {
+  } else {
     const long long wide_tiles = static_cast<long long>((m_local + 255) / 256) * ((n + 511) / 512);
-    if (m_local > 0 && n > 0 && wide_tiles >= 4 * 74 && plan.cta_pair == 2) plan.tile_n = 512;
+    if (m_local > 0 && n > 0 && wide_tiles >= 4 * 74) plan.tile_n = 512;
   }
   return launch_gemmrc_allgather(A_local, B, C_gathered, world, rank, m_local, n, k, plan,
                                  static_cast<cudaStream_t>(stream));

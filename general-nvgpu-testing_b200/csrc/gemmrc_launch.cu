@@ -27,7 +27,6 @@ struct ExtraArgs {
   int flags = 0;
   int fold = 0;
   int bf16 = 0;
-  int gather_box_cols = 0;  // fused all-gather on two-accumulator tiles: 0 / 128 = wide boxes, 64 = swizzled 64-column boxes
   int ldc = 0;  // row pitch of C in elements (0 = n): GEMM-mode kernels store C through a tensor map, so a pitch costs nothing
   const __half* ew_in = nullptr;
   __half* ew_out = nullptr;
@@ -202,19 +201,14 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   st = encode_tmap_2d(&p.tm_b, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k),
                       S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
-  // Fused all-gather: 32 x 128 boxes with plain 256-byte rows (unless the caller asks for the 64-column boxes, and
-  // only with the 3-deep ring, whose two 4 KB staging buffers per warp make one such box).
-  const bool gather_wide = ex.n_peers > 0 && ex.gather_box_cols != 64 && S::kBufsPerWarp == 2;
-  const uint32_t box_cols = gather_wide ? 128 : 64;
   st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
-                      static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, box_cols, !gather_wide);
+                      static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, 64, true);
   if (st != BEAM_OK) return st;
   for (int d = 0; d < ex.n_peers; ++d) {
     st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
-                        static_cast<uint64_t>(n), 32, box_cols, !gather_wide);
+                        static_cast<uint64_t>(n), 32, 64, true);
     if (st != BEAM_OK) return st;
   }
-  p.gather_wide = gather_wide ? 1 : 0;
   p.n_peers = ex.n_peers;
   p.bf16 = ex.bf16;
   p.c = static_cast<__half*>(C);
@@ -450,7 +444,6 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
   ex.bf16 = plan.bf16;
-  ex.gather_box_cols = plan.gather_box_cols;
   if (plan.ldc != 0) {
     if (plan.ldc < n || (plan.ldc % 8) != 0) return BEAM_ERR_INVALID_ARG;  // rows of C must stay 16-byte aligned
     ex.ldc = plan.ldc;

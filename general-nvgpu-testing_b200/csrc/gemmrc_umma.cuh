@@ -76,8 +76,6 @@ struct GemmParams {
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int lead_in;  // two-accumulator tiles: k-blocks issued half-major at the start of a tile (at least 1)
   int lead_out; // ... and at its end
-  int gather_wide;  // fused all-gather on two-accumulator tiles: C leaves as 32 x 128 boxes with 256-byte rows (tm_c and
-                    // tm_peer are then encoded with that box and no swizzle)
   int rb_granules;  // one-kernel split-K: 32-byte granules of every plane per read-back copy (box of tm_peer[0])
   int* status;  // device fault word
 };
@@ -159,19 +157,6 @@ __device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk,
 __device__ __forceinline__ void store_c_box(const GemmParams& p, uint32_t buf, int x, int y) {
   ptx::tma_store_2d_hint(&p.tm_c, buf, x, y, ptx::l2_policy(p.hint_c));
   for (int d = 0; d < p.n_peers; ++d) ptx::tma_store_2d(&p.tm_peer[d], buf, x, y);
-  ptx::tma_store_commit();
-}
-
-// The same with the peers visited in rotated order (`turn` differs from CTA to CTA and from box to box), so that at
-// any instant the CTAs of a GPU spread their stores over all of its outgoing links instead of walking them in step.
-__device__ __forceinline__ void store_c_box_rotated(const GemmParams& p, uint32_t buf, int x, int y, uint32_t turn) {
-  ptx::tma_store_2d_hint(&p.tm_c, buf, x, y, ptx::l2_policy(p.hint_c));
-  const uint32_t n = static_cast<uint32_t>(p.n_peers);
-  uint32_t d = n ? turn % n : 0u;
-  for (uint32_t i = 0; i < n; ++i) {
-    ptx::tma_store_2d(&p.tm_peer[d], buf, x, y);
-    if (++d == n) d = 0;
-  }
   ptx::tma_store_commit();
 }
 

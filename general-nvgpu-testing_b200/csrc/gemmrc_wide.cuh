@@ -274,33 +274,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * h);
       };
-      // Fused all-gather with wide boxes (p.gather_wide): chunks 2h and 2h + 1 of a warp are neighbours in C, so
-      // they leave as ONE box of 32 rows x 128 columns (256-byte rows, no swizzle) from the warp's whole staging area;
-      // NVLink moves 256-byte writes with less overhead than the 128-byte rows of the swizzled 64-column boxes.
-      auto stage_wide = [&](int i) {
-        const int col = tile_col0 + out_col(i & ~1);  // first column of the pair's box
-        const int row = row0 + out_row(i);
-        if (col >= p.n || row >= p.m) return;
-        const uint32_t buf = staging_base + slot * (S::kBufsPerWarp * S::kStoreBufBytes);
-        if ((i & 1) == 0 && store_count > 0) {  // the previous box's stores must have read the buffer
-          if (lane == 0) ptx::tma_store_wait_read<0>();
-          __syncwarp();
-        }
-        // lane = row: 256 bytes per row; this chunk fills the left or the right 128 bytes
-        const uint32_t row_addr = buf + lane * 256u + static_cast<uint32_t>(i & 1) * 128u;
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-          ptx::st_shared_v4(row_addr + static_cast<uint32_t>(jj) * 16u, out[4 * jj], out[4 * jj + 1], out[4 * jj + 2],
-                            out[4 * jj + 3]);
-        if (i & 1) {
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) store_c_box_rotated(p, buf, col, row, (blockIdx.x >> 1) + store_count);
-          ++store_count;
-        }
-      };
       auto stage_and_store = [&](int i) {
-        if (S::kBufsPerWarp == 2 && p.gather_wide) return stage_wide(i);
         const int col = tile_col0 + out_col(i);
         const int row = row0 + out_row(i);
         if (col < p.n && row < p.m) {
@@ -317,7 +291,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
                               out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) store_c_box_rotated(p, buf, col, row, (blockIdx.x >> 1) + store_count);
+          if (lane == 0) store_c_box(p, buf, col, row);
           ++store_count;
         }
       };

@@ -64,9 +64,6 @@ typedef struct beam_gemm_cfg {
   int tiles_in_flight; /* tile_n = 128 with stages = 0 only: 0 or 2 = the CTA (pair) works on two neighbouring tiles at
                          once and alternates its UMMAs between their accumulators (a UMMA of N = 128 is shorter than
                          the wait for its predecessor's result); 1 = one tile at a time                     */
-  int gather_box_cols; /* beam_gemmrc_fp16_allgather on 256 x 512 tiles only: 0 or 128 = every C box leaves as 32 rows x
-                         128 columns with plain 256-byte rows (NVLink carries 256-byte writes with less overhead);
-                         64 = the 32 x 64 swizzled boxes of the single-GPU epilogue                          */
 } beam_gemm_cfg;
 
 /* Split-K only.  The caller guarantees that A and B are not outputs of the kernel that immediately precedes
