@@ -647,19 +647,26 @@ def run_profile_case(args):
     torch.cuda.set_device(0)
     torch.manual_seed(SEED)
     n_launch = max(args.steps, 1)
-    if args.profile in ("gemm", "gemm256", "cublas"):  # cublas: the comparison kernel on the same inputs
+    if args.profile in ("gemm", "gemm256", "gemm128x128", "gemm256x128", "gemm128x128_single", "gemm256x128_single",
+                        "cublas"):  # cublas: the comparison kernel on the same inputs
         a = (torch.randn(M_PER_GPU, K, device="cuda") * 0.1).half()
         b = (torch.randn(N, K, device="cuda") * 0.1).half()
         c = torch.zeros(M_PER_GPU, N, dtype=torch.float16, device="cuda")
         fn = {"cublas": lambda: beam.cublas_gemmexrc(a, b, c),
               "gemm256": lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]),  # one accumulator per tile
+              # the N = 128 families: two tiles in flight (the default) and one tile at a time
+              "gemm128x128": lambda: beam.custom_gemmrc_128x128(a, b, c),
+              "gemm256x128": lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 128]),
+              "gemm128x128_single": lambda: beam.gemmrc(a, b, c, tile_n=128, cta_pair=1, tiles_in_flight=1),
+              "gemm256x128_single": lambda: beam.gemmrc(a, b, c, tile_n=128, cta_pair=2, tiles_in_flight=1),
               "gemm": lambda: beam.cutlass_gemmrc(a, b, c)}[args.profile]
-    elif args.profile in ("splitk", "splitk64"):
-        m, n, k = (128, 256, 65536) if args.profile == "splitk" else (64, 64, 131072)
+    elif args.profile in ("splitk", "splitk64", "splitk_plain", "splitk64_plain"):
+        m, n, k = (128, 256, 65536) if args.profile.startswith("splitk_") or args.profile == "splitk" else (64, 64, 131072)
         a = (torch.rand(m, k, device="cuda") * 2 - 1).half()
         b = (torch.rand(n, k, device="cuda") * 2 - 1).half()
         c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
-        fn = lambda: beam.cutlass_gemmrc_splitk(a, b, c, inputs_stable=True)
+        stable = not args.profile.endswith("_plain")  # "_plain": every call waits for the one before it
+        fn = lambda: beam.cutlass_gemmrc_splitk(a, b, c, inputs_stable=stable)
     else:
         m, n, k = 4096, 4096, 4096
         a = (torch.randn(m, k, device="cuda") * 0.02).half()
@@ -684,7 +691,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the cuBLAS / split-K / LayerNorm side measurements")
-    ap.add_argument("--profile", default=None, choices=["gemm", "gemm256", "cublas", "splitk", "splitk64", "layernorm"],
+    ap.add_argument("--profile", default=None,
+                    choices=["gemm", "gemm256", "gemm128x128", "gemm256x128", "gemm128x128_single", "gemm256x128_single",
+                             "cublas", "splitk", "splitk64", "splitk_plain", "splitk64_plain", "layernorm"],
                     help="run a few launches of one kernel and exit (the command the ncu captures in profiles/ wrap)")
     args = ap.parse_args()
     if args.profile:
