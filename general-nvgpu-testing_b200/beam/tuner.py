@@ -4,8 +4,9 @@
 every candidate on random fp16 inputs, keeps the fastest and caches the answer per shape under the key
 "gemm(M,N,K,)".  What changed:
 
-* the candidates are B200 knobs — UMMA tile N, one CTA or a cta_group::2 pair, TMA ring depth, split-K
-  factor — instead of CUTLASS threadblock/warp shapes (reference :52-94);
+* the candidates are B200 knobs — UMMA tile N, one CTA or a cta_group::2 pair, TMA ring depth, one or two tiles
+  in flight, split-K factor and its one- or two-kernel form — instead of CUTLASS threadblock/warp shapes
+  (reference :52-94);
 * timing uses CUDA events on the current stream with an L2 flush between repetitions (the reference calls
   triton.testing.do_bench, :38-39, which does the same);
 * the "obviously wrong" guard is 1000 TFLOP/s in the reference (:42-43); a B200 exceeds that legitimately,
@@ -129,6 +130,8 @@ class OperatorTuner:
             (128, 1, 4), (128, 1, 6),
         ]
         ret = [Operator(partial(_C.gemmrc, tile_n=tn, cta_pair=cp, stages=st)) for tn, cp, st in search_space]
+        # 128-wide tiles with two tiles in flight per CTA / CTA pair (the default of those families)
+        ret += [Operator(partial(_C.gemmrc, tile_n=128, cta_pair=cp, tiles_in_flight=2)) for cp in (1, 2)]
         # two-accumulator tiles in the other orientation (512 x 256) and without a persistent grid
         ret += [Operator(partial(_C.gemmrc, tile_n=256, tile_m=512, cta_pair=2, stages=st)) for st in (3, 4)]
         ret.append(Operator(partial(_C.gemmrc, tile_n=512, cta_pair=2, stages=3, max_ctas=-1)))
@@ -144,6 +147,13 @@ class OperatorTuner:
             for slices in (0, 4, 8, 16, 32, 64):
                 ret.append(Operator(partial(_C.cutlass_gemmrc_splitk_spec, shape_threadblock=[128, tile_n],
                                             shape_warp=[64, 64], split_k_slices=slices)))
+        # the one-kernel form (cooperative grid, partials summed after a grid-wide barrier) where the library would
+        # launch two kernels by default, and the other way round
+        for tile_n in (64, 128):
+            for slices in (0, 32, 64, 128):
+                for two in (False, True):
+                    ret.append(Operator(partial(_C.cutlass_gemmrc_splitk_spec, shape_threadblock=[128, tile_n],
+                                                shape_warp=[64, 64], split_k_slices=slices, two_kernels=two)))
         return ret
 
     def __init__(self):

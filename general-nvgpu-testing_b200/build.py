@@ -11,6 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbeam_b200.so")
+DRIVER = os.path.join(HERE, "beam_bench")
 SOURCES = ["gemmrc_launch.cu", "splitk_static.cu", "host_entry.cu", "host_common.cc", "beam_api.cc"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
@@ -52,7 +53,23 @@ def build(force=False, verbose=False):
         if r.returncode != 0:
             sys.stderr.write(r.stdout)
             raise RuntimeError("link failed")
+    build_driver(force=force or bool(procs))
     return LIB
+
+
+def build_driver(force=False):
+    """beam_bench: the C++ timing driver (csrc/bench_main.cc), linked against libbeam_b200.so beside it."""
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    src = os.path.join(CSRC, "bench_main.cc")
+    if not force and not _stale(DRIVER, [src, LIB]):
+        return DRIVER
+    cmd = [nvcc, "-std=c++17", "-O2", "-cudart", "static", "-o", DRIVER, src, "-L" + HERE, "-lbeam_b200",
+           "-Xlinker", "-rpath=$ORIGIN", "-lpthread", "-ldl", "-lrt"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("beam_bench link failed")
+    return DRIVER
 
 
 if __name__ == "__main__":

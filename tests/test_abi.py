@@ -130,3 +130,12 @@ def test_splitk_and_layernorm_reject_missing_workspace(lib):
     assert ln(p, p, p, None, p, 1e-5, 64, 64, 64, p, 1 << 16, None) == 1
     assert ln(p, p, p, p, p, 1e-5, 64, 64, 64, None, 0, None) == 4
     assert ln(p, p, p, p, p, 1e-5, 64, 64, 64, p, 16, None) == 4
+
+
+def test_cpp_driver_is_built_and_explains_itself(lib):
+    """build.py links the C++ timing driver next to the library; without arguments that parse it prints its usage."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(lib._name), "beam_bench")
+    assert os.path.exists(exe)
+    r = subprocess.run([exe, "--bogus"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert r.returncode == 1 and "usage: beam_bench" in r.stderr

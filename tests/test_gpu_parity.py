@@ -599,3 +599,23 @@ def test_tuner_picks_a_kernel(beam):
     op, tflops = tuner.tune([2048, 2048, 2048])
     assert op is not None and 1.0 < tflops < 2500.0
     assert tuner.tune([2048, 2048, 2048]) == (op, tflops)
+
+
+def test_cpp_timing_driver(beam):
+    """beam_bench (csrc/bench_main.cc) times registry kernels from C++ through the C ABI with the reference's
+    test_pipeline scheme (cuda/cublas.cc:12-40): it must run the kernels it names and report a healthy device."""
+    import json
+    import subprocess
+    exe = os.path.join(os.path.dirname(beam.library_path()), "beam_bench")
+    assert os.path.exists(exe), "beam_bench is built next to libbeam_b200.so by build.py"
+    for extra in (["--kernel", "cutlass_gemmrc", "--m", "1024", "--n", "1024", "--k", "1024", "--nrep", "3"],
+                  ["--kernel", "cutlass_gemmrc_spec", "--tb_m", "256", "--tb_n", "128", "--m", "768", "--n", "520", "--k", "264"],
+                  ["--kernel", "cutlass_gemmrc_splitk", "--m", "128", "--n", "256", "--k", "8192", "--nrep", "4"],
+                  ["--kernel", "cutlass_gemmrc_splitk", "--m", "64", "--n", "64", "--k", "16384", "--stable", "1", "--sets", "2"]):
+        r = subprocess.run([exe] + extra, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr
+        line = json.loads(r.stdout.strip().splitlines()[-1])
+        assert line["device_status"] == 0 and line["fault_word"] == 0 and line["us_per_call"] > 0
+    r = subprocess.run([exe, "--kernel", "no_such_kernel", "--m", "64", "--n", "64", "--k", "64"], stdout=subprocess.PIPE,
+                       stderr=subprocess.PIPE, text=True, timeout=120)
+    assert r.returncode == 3 and "invalid argument" in r.stderr
