@@ -507,8 +507,13 @@ def run_ours(args):
     per_gpu = value / world
 
     # ---- e2e: host buffers through the host entry, copies inside the timed region
+    # (host buffers are allocated after binding the rank to its GPU's NUMA node, so that they are local to its PCIe root)
+    from beam.sharded import bind_to_gpu_numa_node
+    cpus_before = os.sched_getaffinity(0)
+    numa_bound = bind_to_gpu_numa_node(local)
     ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
-    hc = torch.empty(M_PER_GPU, N, dtype=torch.float16).pin_memory()
+    hc = torch.zeros(M_PER_GPU, N, dtype=torch.float16).pin_memory()  # zeros: the pages are touched here
+    os.sched_setaffinity(0, cpus_before)  # only the allocations above needed the binding
     if world > 1:
         # Every rank holds A_local and all of B on the host; rank r uploads 1/world of B and the ranks all-gather it
         # over NVLink, so B crosses PCIe once per step for the whole job instead of once per rank.
@@ -605,6 +610,7 @@ def run_ours(args):
                              "become computable" if world == 1 else
                              "beam.sharded.ShardedHostGemm: each rank uploads its rows of A and 1/%d of B, B is "
                              "all-gathered over NVLink (NCCL), C rows come back; per step" % world),
+                    "host_buffers_numa_local": bool(numa_bound),
                     "timer": "host clock around the blocking call (copies and kernels on internal streams)"},
             "gpu_launches": args.steps,
             "clocks": clk.summary(),

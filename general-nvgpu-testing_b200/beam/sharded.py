@@ -96,6 +96,45 @@ def gemmrc_allgather(a_local: torch.Tensor, b: torch.Tensor, gathered: "Gathered
     return gathered.tensor
 
 
+def bind_to_gpu_numa_node(device_index: Optional[int] = None) -> bool:
+    """Pins the calling process to the CPUs that NVML names as closest to the GPU (its NUMA node), so that host
+    buffers allocated and first touched afterwards (pinned staging memory in particular) are local to the GPU's PCIe
+    root.  On a two-socket host an unbound rank otherwise allocates wherever it happens to run, and every copy then
+    crosses the socket interconnect.  Reads NVML and changes this process's own CPU affinity, nothing on the GPU.
+    Returns False (and changes nothing) when NVML or the affinity call is unavailable."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        if device_index is None:
+            device_index = torch.cuda.current_device()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            try:
+                device_index = int(visible.split(",")[device_index])
+            except (ValueError, IndexError):
+                pass
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, bits in enumerate(mask) for b in range(64) if (int(bits) >> b) & 1}
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return False
+        os.sched_setaffinity(0, allowed)
+        return True
+    except Exception:
+        return False
+
+
+def b_shard_rows(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """[start, stop) of the rows of B that rank `rank` uploads in ShardedHostGemm (equal shards)."""
+    if world <= 0 or not (0 <= rank < world) or n % world != 0:
+        raise ValueError("N=%d does not divide over world=%d (rank %d)" % (n, world, rank))
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
 class ShardedHostGemm:
     """Row-sharded rc GEMM for operands that live in HOST memory on every rank: C_local = A_local @ B.T.
 
@@ -118,8 +157,7 @@ class ShardedHostGemm:
 
     def shard_rows(self) -> Tuple[int, int]:
         """[start, stop) of the rows of B this rank uploads."""
-        per = self.n // self.world
-        return self.rank * per, (self.rank + 1) * per
+        return b_shard_rows(self.n, self.world, self.rank)
 
     def __call__(self, a_local_host: torch.Tensor, b_host: torch.Tensor, c_local_host: torch.Tensor) -> None:
         """b_host is the whole B on the host (every rank has it); only this rank's shard of it is read."""

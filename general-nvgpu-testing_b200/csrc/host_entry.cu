@@ -43,12 +43,20 @@ int grow(void** p, size_t* cap, size_t need) {
   return BEAM_OK;
 }
 
-// Rows per block: about an eighth of the dimension, a multiple of 256 (a pair tile), so that at most kMaxSteps / 2
-// blocks cover it.
+// Rows per block: about an eighth of the dimension, a multiple of 256 (a pair tile), so that fewer than
+// kMaxSteps / 2 blocks cover it (the last regular block is cut in two, see next_block).
 int block_rows(int dim) {
   int rows = ((dim + 7) / 8 + 255) / 256 * 256;
-  while ((dim + rows - 1) / rows > HostPath::kMaxSteps / 2) rows *= 2;
+  while ((dim + rows - 1) / rows + 1 > HostPath::kMaxSteps / 2) rows *= 2;
   return rows;
+}
+
+// Rows of the next block when `left` rows remain: the regular block, except that the last regular block is cut in
+// two, so that the strip whose copy back nothing overlaps any more (the last one) is half as long.
+int next_block(int left, int blk) {
+  if (left > blk) return blk;
+  const int half = ((left + 1) / 2 + 255) / 256 * 256;
+  return (left > 512 && half < left) ? half : left;
 }
 
 // The body of a call; any failure leaves work in flight on the internal streams, which the caller drains.
@@ -70,7 +78,7 @@ int run_pipeline(HostPath& h, const void* A_host, const void* B_host, const void
     // B goes first and the two alternate while both have rows left (the computable area stays close to a square).
     const bool take_b = b_done < n && (a_done >= m || b_done <= a_done);
     const int r0 = take_b ? b_done : a_done;
-    const int rows = take_b ? (n - r0 < blk_b ? n - r0 : blk_b) : (m - r0 < blk_a ? m - r0 : blk_a);
+    const int rows = next_block(take_b ? n - r0 : m - r0, take_b ? blk_b : blk_a);
     const char* src = static_cast<const char*>(take_b ? B_host : A_host) + static_cast<size_t>(r0) * row_a;
     char* dst = (take_b ? static_cast<char*>(h.dB) : static_cast<char*>(h.dA)) + static_cast<size_t>(r0) * row_a;
     BEAM_CUDA_TRY(cudaMemcpyAsync(dst, src, static_cast<size_t>(rows) * row_a, cudaMemcpyHostToDevice, h.s_in), "H2D");

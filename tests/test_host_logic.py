@@ -179,3 +179,28 @@ def test_row_sharded_gemm_two_gloo_ranks(tmp_path):
     world = 2
     mp.spawn(_gloo_worker, args=(world, _free_port(), 64, 37, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def test_b_shards_cover_b_exactly():
+    """ShardedHostGemm uploads disjoint, equal shards of B that together are all of B; uneven splits are refused."""
+    from beam.sharded import b_shard_rows
+    for n, world in ((8192, 8), (1024, 2), (520, 1), (4096, 4)):
+        spans = [b_shard_rows(n, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        assert len({e - s for s, e in spans}) == 1
+    with pytest.raises(ValueError):
+        b_shard_rows(1000, 3, 0)
+    with pytest.raises(ValueError):
+        b_shard_rows(1024, 2, 2)
+
+
+def test_numa_binding_is_harmless_without_a_gpu():
+    """bind_to_gpu_numa_node only ever narrows this process's own CPU affinity and reports False when it cannot ask
+    NVML (no driver in this container): the affinity must be unchanged then."""
+    from beam.sharded import bind_to_gpu_numa_node
+    before = os.sched_getaffinity(0)
+    ok = bind_to_gpu_numa_node(0)
+    after = os.sched_getaffinity(0)
+    assert after <= before and (ok or after == before)
+    os.sched_setaffinity(0, before)
