@@ -3,15 +3,18 @@
 // A tcgen05.mma of N = 128, K = 16 is 64 clocks of tensor-pipe work, but consecutive UMMAs into the SAME
 // accumulator retire only about every 120 clocks: the next one needs the previous result.  With one tile per
 // CTA every instruction of the main loop targets the same accumulator, and the pipe idles for nearly half of
-// the time.  Here a CTA (pair) works on two neighbouring output tiles at once: a shared-memory stage carries one
-// k-block of both tiles (A and B boxes of each, loaded independently), and the issuer alternates, instruction by
-// instruction, between the two tiles' accumulators, so that an accumulator is revisited only every second
-// instruction.  TMEM holds four 128-column accumulators: two being computed, two being drained by the epilogue.
+// the time.  Here a CTA (pair) works on two output tiles at once, the two vertically adjacent tiles of one N
+// column: the issuer alternates, instruction by instruction, between the two tiles' accumulators, so that an
+// accumulator is revisited only every second instruction.  TMEM holds four 128-column accumulators: two being
+// computed, two being drained by the epilogue.
 //
-// Roles, barriers, staging and the TMA-store epilogue are those of gemmrc_umma_kernel in GEMM mode.  The two
-// tiles of a work item are consecutive in the grouped raster (same N tile, adjacent M tiles inside a group), so
-// their B boxes are the same lines in L2.  When the tile count is odd the last item's second tile does not exist:
-// its loads fall outside the tensors (zero fill), its products are zeros and its stores are skipped.
+// Both tiles multiply by the same rows of B, so a shared-memory stage carries the A box of each tile and ONE B box
+// (a 128 x 128 tile needs 128 bytes per clock per SM from L2 at full tensor rate, which is all the L2 -> SM port
+// delivers; sharing B brings the pair down to 96).  Work items are therefore pairs of tiles ("double tiles" of
+// 2 x 128 x kCta rows), walked in the grouped raster of gemmrc_umma_kernel.  With an odd number of tile rows the
+// last double tile's second tile lies below the matrix: its A box loads as zeros and its stores are skipped.
+//
+// Roles, barriers, staging and the TMA-store epilogue are those of gemmrc_umma_kernel in GEMM mode.
 #pragma once
 
 #include "gemmrc_umma.cuh"
@@ -26,8 +29,7 @@ struct DualShape {
   static constexpr int kBRows = kBN / kCta;
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = kBRows * kBK * 2;
-  static constexpr int kTileBytes = kABytes + kBBytes;  // one tile's k-block in one CTA
-  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kStageBytes = 2 * kABytes + kBBytes;  // [A of tile 0][A of tile 1][B, shared by both]
   static constexpr int kTmemCols = 4 * kBN;
   static constexpr int kBarBytes = 512;
   static constexpr int kStoreBufBytes = 32 * 128;
@@ -37,28 +39,23 @@ struct DualShape {
   static constexpr int kThreads = 192;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static_assert((2 * kStages + 4) * 8 + 32 <= kBarBytes, "barrier block too small");
-  static_assert(kTileBytes % 1024 == 0, "tile buffers must keep the 1024-byte alignment of the swizzle atom");
+  static_assert(kABytes % 1024 == 0 && kBBytes % 1024 == 0, "boxes must keep the 1024-byte alignment of the swizzle atom");
 };
 
-// Tile `t` of the grouped raster (see work_item in gemmrc_umma.cuh); a tile index past the end maps to the row of
-// tiles below the matrix, which loads as zeros and stores nothing.
-__device__ __forceinline__ void dual_tile_coords(const GemmParams& p, int t, int& mt, int& nt) {
-  if (t >= p.m_tiles * p.n_tiles) {
-    mt = p.m_tiles;
-    nt = 0;
-    return;
-  }
+// Double tile `t` of the grouped raster (see work_item in gemmrc_umma.cuh; p.m_tiles counts double tiles here).
+__device__ __forceinline__ void dual_item_coords(const GemmParams& p, int t, int& mt2, int& nt) {
   const int per_group = p.group_m * p.n_tiles;
   const int g = t / per_group;
   const int first_m = g * p.group_m;
   const int rows = min(p.group_m, p.m_tiles - first_m);
   const int r = t - g * per_group;
-  mt = first_m + r % rows;
+  mt2 = first_m + r % rows;
   nt = r / rows;
 }
 
 namespace ptx {
-// One 64-wide k-block of two tiles: eight UMMAs (K = 16 each), alternating between the two accumulators.
+// One 64-wide k-block of two tiles: eight UMMAs (K = 16 each), alternating between the two accumulators (the two
+// B descriptors may be the same operand).
 template <int kCta>
 __device__ __forceinline__ void umma_f16_kblock_two_tiles(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t b0,
                                                           uint64_t a1, uint64_t b1, uint32_t idesc,
@@ -111,15 +108,15 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
   const bool leader = cta_rank == 0;
   const int stride = (kCta == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const int first = (kCta == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int items = (p.m_tiles * p.n_tiles + 1) / 2;  // work items of two tiles each
+  const int items = p.m_tiles * p.n_tiles;  // double tiles
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t staging_base = smem_base + kStages * S::kStageBytes;
   const uint32_t bar_base = staging_base + S::kStagingBytes;
-  // stage s = [A of tile 0][B of tile 0][A of tile 1][B of tile 1]
-  auto smem_a = [&](int s, int h) { return smem_base + s * S::kStageBytes + h * S::kTileBytes; };
-  auto smem_b = [&](int s, int h) { return smem_a(s, h) + S::kABytes; };
+  // stage s = [A of tile 0][A of tile 1][B]
+  auto smem_a = [&](int s, int h) { return smem_base + s * S::kStageBytes + h * S::kABytes; };
+  auto smem_b = [&](int s) { return smem_base + s * S::kStageBytes + 2 * S::kABytes; };
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
@@ -162,14 +159,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       for (int j = 0; alive && first + j * stride < items; ++j) {
-        const int t0 = 2 * (first + j * stride);
-        int row_a[2], row_b[2];
-        for (int h = 0; h < 2; ++h) {
-          int mt, nt;
-          dual_tile_coords(p, t0 + h, mt, nt);
-          row_a[h] = mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
-          row_b[h] = nt * S::kBN + static_cast<int>(cta_rank) * S::kBRows;
-        }
+        int mt2, nt;
+        dual_item_coords(p, first + j * stride, mt2, nt);
+        int row_a[2];
+        for (int h = 0; h < 2; ++h) row_a[h] = (2 * mt2 + h) * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
+        const int row_b = nt * S::kBN + static_cast<int>(cta_rank) * S::kBRows;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -179,18 +173,16 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
           }
           if constexpr (kCta == 1) {
             ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 2; ++h)
               ptx::tma_load_2d_hint(smem_a(s, h), &p.tm_a, full_bar(s), kb * S::kBK, row_a[h], pol_a);
-              ptx::tma_load_2d_hint(smem_b(s, h), &p.tm_b, full_bar(s), kb * S::kBK, row_b[h], pol_b);
-            }
+            ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
             const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 2; ++h)
               ptx::tma_load_2d_pair_hint(smem_a(s, h), &p.tm_a, lead_bar, kb * S::kBK, row_a[h], pol_a);
-              ptx::tma_load_2d_pair_hint(smem_b(s, h), &p.tm_b, lead_bar, kb * S::kBK, row_b[h], pol_b);
-            }
+            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b, lead_bar, kb * S::kBK, row_b, pol_b);
           }
         }
       }
@@ -201,9 +193,9 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
       const uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, S::kBN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       uint32_t stage = 0, parity = 0;
       const uint64_t a_desc0 = ptx::umma_desc_k_sw128(smem_a(0, 0));
-      const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0, 0));
+      const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0));
       constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
-      constexpr uint64_t kDescTile = static_cast<uint64_t>(S::kTileBytes >> 4);
+      constexpr uint64_t kDescTile = static_cast<uint64_t>(S::kABytes >> 4);  // from tile 0's A box to tile 1's
       bool alive = true;
       for (int j = 0; alive && first + j * stride < items; ++j) {
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;  // which pair of accumulators
@@ -220,8 +212,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
           ptx::tc_fence_after();
           const uint64_t a0 = a_desc0 + stage * kDescStride;
           const uint64_t b0 = b_desc0 + stage * kDescStride;
-          ptx::umma_f16_kblock_two_tiles<kCta>(d0, d1, a0, b0, a0 + kDescTile, b0 + kDescTile, idesc,
-                                               kb > 0 ? 1u : 0u);
+          ptx::umma_f16_kblock_two_tiles<kCta>(d0, d1, a0, b0, a0 + kDescTile, b0, idesc, kb > 0 ? 1u : 0u);
           if constexpr (kCta == 1)
             ptx::umma_commit<1>(empty_bar(stage));
           else
@@ -249,12 +240,11 @@ __global__ void __launch_bounds__(192, 1) gemmrc_dual_kernel(const __grid_consta
       const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
       if (!bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane)) break;
       ptx::tc_fence_after();
-      const int t0 = 2 * (first + j * stride);
+      int mt2, nt;
+      dual_item_coords(p, first + j * stride, mt2, nt);
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
-        int mt, nt;
-        dual_tile_coords(p, t0 + h, mt, nt);
-        const int box_y = mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
+        const int box_y = (2 * mt2 + h) * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM + static_cast<int>(quad) * 32;
         const int col0 = nt * S::kBN;
         const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + (acc * 2u + static_cast<uint32_t>(h)) * S::kBN;
 #pragma unroll 1

@@ -289,15 +289,15 @@ int launch_dual_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   p.n = n;
   p.k = k;
   p.ldc = n;
-  p.m_tiles = (m + S::kBM * kCta - 1) / (S::kBM * kCta);
+  p.m_tiles = (m + 2 * S::kBM * kCta - 1) / (2 * S::kBM * kCta);  // double tiles: two vertically adjacent tiles each
   p.n_tiles = (n + S::kBN - 1) / S::kBN;
-  p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 8 : 16);
+  p.group_m = group_m > 0 ? group_m : (kCta == 2 ? 4 : 8);
   p.slices = 1;
   p.hint_a = (ex.l2_hints / 10) % 10;
   p.hint_b = ex.l2_hints % 10;
   p.hint_c = (ex.l2_hints / 100) % 10;
   p.status = ctx->status_word;
-  const long long items = (static_cast<long long>(p.m_tiles) * p.n_tiles + 1) / 2;
+  const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles;
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
   if (items < clusters) clusters = static_cast<int>(items);
@@ -466,7 +466,7 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
     // 128-wide tiles: two tiles in flight per CTA (pair), so that consecutive UMMAs never target one accumulator
     if (plan.cta_pair == 2)
       return launch_dual_instance<4, 2>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
-    return launch_dual_instance<3, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
+    return launch_dual_instance<4, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
   }
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
