@@ -463,7 +463,7 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
     return BEAM_ERR_UNSUPPORTED;
   }
   if (plan.tile_n == 128 && plan.stages == 0 && plan.tiles_in_flight != 1) {
-    // 128-wide tiles: two tiles in flight per CTA (pair), so that consecutive UMMAs never target one accumulator
+    // 128-wide tiles: two tiles in flight per CTA (pair), each with its own accumulator and issuing thread
     if (plan.cta_pair == 2)
       return launch_dual_instance<4, 2>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return launch_dual_instance<4, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
