@@ -328,7 +328,7 @@ def cutlass_parallel_gemmrc_silu(a, b, c, x, y):
         _raise(st, "beam_gemmrc_silu")
 
 
-def gemmrc_allgather(a_local, b, gathered_ptrs, rank, n, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0):
+def gemmrc_allgather(a_local, b, gathered_ptrs, rank, n, tile_n=0, cta_pair=0, stages=0, group_m=0):
     """Fused row-sharded GEMM + all-gather: this rank's a_local[M_local,K] @ b[N,K].T is written into row block `rank`
     of every rank's gathered C[world * M_local, N]; gathered_ptrs[d] is rank d's buffer as a device pointer valid in
     this process (see beam.sharded.GatheredC).  Asynchronous; complete once all ranks' kernels have finished."""
@@ -342,8 +342,8 @@ def gemmrc_allgather(a_local, b, gathered_ptrs, rank, n, tile_n=0, cta_pair=0, s
     world = len(gathered_ptrs)
     arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in gathered_ptrs])
     cfg = None
-    if tile_n or cta_pair or stages or group_m or max_ctas:
-        cfg = ctypes.byref(beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas)))
+    if tile_n or cta_pair or stages or group_m:
+        cfg = ctypes.byref(beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m)))
     L = _load()
     with torch.cuda.device(a_local.device):
         st = L.beam_gemmrc_fp16_allgather(a_local.data_ptr(), b.data_ptr(), arr, world, int(rank), int(m), int(n), int(k),

@@ -73,7 +73,6 @@ int beam_gemmrc_fp16_allgather(const void* A_local, const void* B, void* const* 
     if (cfg->cta_pair) plan.cta_pair = cfg->cta_pair;
     plan.stages = cfg->stages;
     plan.group_m = cfg->group_m;
-    plan.gather_deep = cfg->max_ctas == -2 ? 1 : 0;  // experiment switch
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
     if (plan.stages < 0 || plan.group_m < 0) return BEAM_ERR_INVALID_ARG;
   }

@@ -96,11 +96,11 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
                       fold ? S::kBRows / 2 : S::kBRows, S::kBK, true);
   if (st != BEAM_OK) return st;
   p.fold = fold ? 1 : 0;
-  p.bf16 = (kMode == kModeGemm || kMode == kModeGemmGather) ? ex.bf16 : 0;
+  p.bf16 = (kMode == kModeGemm) ? ex.bf16 : 0;
   p.ew_in = ex.ew_in;
   p.ew_out = ex.ew_out;
   p.ew_count = ex.ew_count;
-  if (kMode == kModeGemm || kMode == kModeGemmSilu || kMode == kModeGemmGather) {
+  if (kMode == kModeGemm || kMode == kModeGemmSilu) {
     st = encode_tmap_2d(&p.tm_c, C, 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
                         static_cast<uint64_t>(ex.ldc > 0 ? ex.ldc : n), 32, 64, true);
   } else {
@@ -109,7 +109,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
                             static_cast<uint64_t>(n), 32, 32);
   }
   if (st != BEAM_OK) return st;
-  if (kMode == kModeGemm || kMode == kModeGemmGather) {
+  if (kMode == kModeGemm) {
     for (int d = 0; d < ex.n_peers; ++d) {
       st = encode_tmap_2d(&p.tm_peer[d], ex.peer_c[d], 2, static_cast<uint64_t>(m), static_cast<uint64_t>(n),
                           static_cast<uint64_t>(n), 32, 64, true);
@@ -468,8 +468,6 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
       return launch_dual_instance<4, 2>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return launch_dual_instance<4, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
   }
-  if (ex.n_peers > 0 && plan.tile_n == 256 && plan.cta_pair == 2 && plan.stages == 0 && plan.gather_deep)
-    return launch_instance<256, 4, 2, kModeGemmGather>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
   BEAM_GEMM_CASE(256, 6, 2)

@@ -21,8 +21,6 @@
 //
 // Three epilogues share this pipeline:
 //   kModeGemm       fp32 -> fp16, store C.
-//   kModeGemmGather the same with six staging buffers per epilogue warp instead of two (and a shallower operand ring):
-//                   for the fused all-gather, whose stores to peer GPUs drain at NVLink rate.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
 //                   (Calls whose work items fit on the device at once run as one kernel instead: splitk_stream.cuh.)
@@ -42,7 +40,7 @@
 
 namespace beam {
 
-enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3, kModeGemmGather = 4 };
+enum GemmMode : int { kModeGemm = 0, kModeSplitK = 1, kModeLayerNorm = 2, kModeGemmSilu = 3 };
 __host__ __device__ constexpr bool is_splitk_mode(int mode) { return mode == kModeSplitK; }
 
 struct GemmParams {
@@ -95,7 +93,7 @@ struct GemmShape {
   static constexpr int kStoreBufBytes = 32 * 128;  // one warp's box: 32 rows x 128 bytes
   // Staging buffers per epilogue warp: two for the output stores; LayerNorm keeps four, which also serve
   // as the landing ring of its second pass.
-  static constexpr int kBufsPerWarp = (kMode == kModeLayerNorm) ? 4 : (kMode == kModeGemmGather ? 6 : 2);
+  static constexpr int kBufsPerWarp = (kMode == kModeLayerNorm) ? 4 : 2;
   static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kThreads = 192;
@@ -643,7 +641,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
       float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm: this row's statistics over this tile
       // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
-      constexpr bool kHalfOut = (kMode == kModeGemm || kMode == kModeGemmSilu || kMode == kModeGemmGather);  // fp16 C through tm_c
+      constexpr bool kHalfOut = (kMode == kModeGemm || kMode == kModeGemmSilu);  // fp16 C through tm_c
       constexpr int kChunkCols = kHalfOut ? 64 : 32;
       // Folded split-K: lanes 0..63 own the block in TMEM columns 0..63, lanes 64..127 the one in columns 64..127.
       const int fold_half = fold ? static_cast<int>(quad >> 1) : 0;
