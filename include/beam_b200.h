@@ -141,9 +141,10 @@ BEAM_API int beam_cutlass_gemmrc_spec(const void* A, const void* B, void* C, int
  * pick"; pass the same values as to the entry point. */
 BEAM_API size_t beam_gemmrc_splitk_workspace_bytes(int m, int n, int k, int tile_n, int split_k_slices);
 
-/* The split factor the heuristic picks for this tile_n (0 = default tile): one work item per SM, at
- * least 256 of K per slice.  Replaces get_slice_heuristic (cuda/cutlass_kernels/
- * cutlass_gemmrc_splitk.cu:44-57), which models the 108 SMs of an A100. */
+/* The split factor the heuristic picks for this tile_n (0 = default tile) for a plain call on the current device:
+ * work items for about two thirds of the SMs (seven eighths for folded problems, M and N <= 64), at least 256 of K
+ * per slice; values measured on B200 with chains of dependent calls.  Replaces get_slice_heuristic
+ * (cuda/cutlass_kernels/cutlass_gemmrc_splitk.cu:44-57), which models the 108 SMs of an A100. */
 BEAM_API int beam_gemmrc_splitk_heuristic(int m, int n, int k, int tile_n);
 
 /* How a split-K call with these arguments runs on the current device: info[0] = tile N, info[1] = K slices,
