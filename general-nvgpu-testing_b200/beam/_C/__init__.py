@@ -207,13 +207,15 @@ def cutlass_gemmrc_spec(a, b, c, shape_threadblock=[128, 128], shape_warp=[64, 6
     _run("beam_cutlass_gemmrc_spec", a, b, c, tbm, tbn, wm, wn)
 
 
-def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, tile_m=0, tiles_in_flight=0):
+def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hints=0, tile_m=0, tiles_in_flight=0,
+           whole_tiles=False):
     """c = a @ b.T with explicit Blackwell knobs (0 = default); what the tuner searches over.  The three tensors may
-    be bfloat16 instead of float16 (all three alike)."""
+    be bfloat16 instead of float16 (all three alike).  whole_tiles=True keeps the last wave's 256 x 256 tiles whole
+    instead of cutting them into 128-column halves (a cut tile sums K in a different, equally fixed order)."""
     m, n, k = _check_abc(a, b, c, allow_bf16=True)
     if not (a.dtype == b.dtype == c.dtype):
         raise TypeError("a, b, c must share one dtype")
-    flags = 2 if a.dtype == torch.bfloat16 else 0
+    flags = (2 if a.dtype == torch.bfloat16 else 0) | (FLAG_WHOLE_TILES if whole_tiles else 0)
     cfg = beam_gemm_cfg(int(tile_n), int(cta_pair), int(stages), int(group_m), 0, int(max_ctas), int(l2_hints), flags,
                         int(tile_m), int(tiles_in_flight))
     L = _load()
@@ -226,6 +228,7 @@ def gemmrc(a, b, c, tile_n=0, cta_pair=0, stages=0, group_m=0, max_ctas=0, l2_hi
 FLAG_INPUTS_STABLE = 1
 FLAG_SPLITK_TWO_KERNELS = 4
 FLAG_SPLITK_ONE_KERNEL = 8
+FLAG_WHOLE_TILES = 16
 
 
 def _splitk_flags(inputs_stable, two_kernels):

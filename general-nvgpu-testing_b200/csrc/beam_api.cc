@@ -53,11 +53,12 @@ int beam_gemmrc_fp16(const void* A, const void* B, void* C, int m, int n, int k,
     plan.max_ctas = cfg->max_ctas;
     plan.l2_hints = cfg->l2_hints;
     plan.bf16 = (cfg->flags & BEAM_FLAG_BF16) ? 1 : 0;
+    plan.whole_tiles = (cfg->flags & BEAM_FLAG_WHOLE_TILES) ? 1 : 0;
     plan.tile_m = cfg->tile_m;
     plan.tiles_in_flight = cfg->tiles_in_flight;
     if (plan.tiles_in_flight < 0 || plan.tiles_in_flight > 2) return BEAM_ERR_INVALID_ARG;
     if (plan.tile_m != 0 && plan.tile_m != 512) return BEAM_ERR_INVALID_ARG;
-    if (cfg->flags & ~(BEAM_FLAG_BF16)) return BEAM_ERR_INVALID_ARG;
+    if (cfg->flags & ~(BEAM_FLAG_BF16 | BEAM_FLAG_WHOLE_TILES)) return BEAM_ERR_INVALID_ARG;
     if (plan.cta_pair != 1 && plan.cta_pair != 2) return BEAM_ERR_INVALID_ARG;
     if (plan.stages < 0 || plan.group_m < 0 || plan.max_ctas < -1 || plan.l2_hints < 0 || plan.l2_hints > 333)
       return BEAM_ERR_INVALID_ARG;

@@ -94,6 +94,10 @@ __global__ void __launch_bounds__(224, 1) gemmrc_dual_kernel(const __grid_consta
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
     ptx::prefetch_tensormap(&p.tm_c);
+    // A programmatic dependent of the kernel before it on the stream: the set-up above may overlap that kernel's last
+    // CTAs; no thread touches global memory before that grid has completed (the barrier below follows this wait).
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
   }
   if (warp == 1) {
     ptx::tmem_alloc<kCta>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);

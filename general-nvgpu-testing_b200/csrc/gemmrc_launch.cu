@@ -27,6 +27,7 @@ struct ExtraArgs {
   int flags = 0;
   int fold = 0;
   int bf16 = 0;
+  int whole_tiles = 0;  // 1 = never cut the tiles of the last wave in two (256 x 256 tiles on pairs)
   int ldc = 0;  // row pitch of C in elements (0 = n): GEMM-mode kernels store C through a tensor map, so a pitch costs nothing
   const __half* ew_in = nullptr;
   __half* ew_out = nullptr;
@@ -140,9 +141,22 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   p.flags = ex.flags;
   p.status = ctx->status_word;
 
-  const long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
+  long long items = static_cast<long long>(p.m_tiles) * p.n_tiles * p.slices;
   int clusters = resident;
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
+  if (S::kCutTiles) {
+    // The last wave of the persistent grid: when its tiles occupy at most half of the pairs, they are cut into
+    // 128-column halves, which occupy twice as many pairs for about half as long (4096^3: 256 tiles on 74 pairs are
+    // 3 waves and 34 tiles; as 68 halves those take 0.6 of a wave instead of a whole one).
+    st = encode_tmap_2d(&p.tm_b_tail, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                        static_cast<uint64_t>(k), S::kBRows / 2, S::kBK, true);
+    if (st != BEAM_OK) return st;
+    const int last_wave = static_cast<int>(items % clusters);
+    if (!ex.whole_tiles && last_wave > 0 && 2 * last_wave <= clusters && n > BN / 2 && k > 64) {
+      p.tail_tiles = last_wave;
+      items += last_wave;
+    }
+  }
   if (items < clusters) clusters = static_cast<int>(items);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCta), 1, 1);
@@ -162,7 +176,7 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
     attr[cfg.numAttrs].val.cooperative = 1;
     ++cfg.numAttrs;
   }
-  if (is_splitk_mode(kMode)) {
+  if (is_splitk_mode(kMode) || kMode == kModeGemm) {
     // May start while the previous kernel on the stream drains; the kernel itself waits for that grid's
     // completion before its first global read or write.
     attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -236,13 +250,16 @@ int launch_wide_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // a programmatic dependent of the kernel before it: set-up overlaps that kernel's tail (the kernel waits for it)
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_wide)");
   return BEAM_OK;
 }
@@ -306,13 +323,15 @@ int launch_dual_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, 
   cfg.blockDim = dim3(S::kThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kCta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p), "cudaLaunchKernelEx(gemmrc_dual)");
   return BEAM_OK;
 }
@@ -444,6 +463,7 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
   const int stages = plan.stages > 0 ? plan.stages : default_stages(plan.tile_n, plan.cta_pair);
   ex.l2_hints = plan.l2_hints;
   ex.bf16 = plan.bf16;
+  ex.whole_tiles = plan.whole_tiles;
   if (plan.ldc != 0) {
     if (plan.ldc < n || (plan.ldc % 8) != 0) return BEAM_ERR_INVALID_ARG;  // rows of C must stay 16-byte aligned
     ex.ldc = plan.ldc;
@@ -537,6 +557,22 @@ int splitk_tile_n(int n, int tile_n) {
   return n <= 64 ? 64 : 128;
 }
 
+// Split-K serves two kinds of problem.  Small M and N (the reference's 128 x 256 x 65536 and 64 x 64 x 131072) stream A
+// and B once and are bound by HBM.  Medium M and N (512 x 512 x 8192, python/gemm_test.py:201 of the reference;
+// 1024 x 1024 x 8192) have too few output tiles for the SMs but more arithmetic than memory time: with every SM at work
+// 2 M N K flop take longer than 2 K (M + N) bytes once M N / (M + N) exceeds about 200 (B200: ~1500 TFLOP/s against
+// ~6.5 TB/s).  Those want the 256-wide tile (UMMAs of N = 256 keep the tensor pipe busy from one issuing thread,
+// N = 128 ones do not) and as many slices as fill the SMs.
+bool splitk_compute_bound(int m, int n) {
+  return static_cast<double>(m) * n >= 200.0 * (static_cast<double>(m) + n);
+}
+
+int splitk_pick_tile(int m, int n, int tile_n) {
+  if (tile_n == 64 || tile_n == 128 || tile_n == 256) return tile_n;
+  if (n >= 256 && splitk_compute_bound(m, n)) return 256;
+  return splitk_tile_n(n, 0);
+}
+
 // Plain calls (each call waits for the one before it), measured on B200 with chains of dependent calls over
 // HBM-cold inputs: two thirds of the SMs get a work item (128 x 256 x 65536: 16.1 us with 96 CTAs against 17.3 to
 // 18.8 with 128 to 148; fewer CTAs drain sooner and the memory system is saturated either way); folded problems
@@ -549,7 +585,7 @@ int splitk_tile_n(int n, int tile_n) {
 // for two or three consecutive calls to stream side by side (measured optimum on B200 for 128x256x65536 and
 // 64x64x131072).
 int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
-  const int bn = splitk_tile_n(n, tile_n);
+  const int bn = splitk_pick_tile(m, n, tile_n);
   const long long m_tiles = (m + 127) / 128, n_tiles = (n + bn - 1) / bn;
   const long long tiles = m_tiles * n_tiles;
   const int num_kb = (k + 63) / 64;
@@ -573,7 +609,12 @@ int splitk_heuristic(int m, int n, int k, int tile_n, int flags) {
     const long long by_bytes = static_cast<long long>(bytes / per_cta / static_cast<double>(tiles) + 0.5);
     if (by_bytes < s) s = by_bytes;
   }
-  const long long cap = num_kb / 4 > 0 ? num_kb / 4 : 1;
+  long long cap = num_kb / 4 > 0 ? num_kb / 4 : 1;
+  if (!folds && splitk_compute_bound(m, n)) {
+    // every SM a work item; slices of at least 8 k-blocks, so that a slice's arithmetic outweighs its partial plane
+    s = sms / (tiles > 0 ? tiles : 1);
+    cap = num_kb / 8 > 0 ? num_kb / 8 : 1;
+  }
   if (s > cap) s = cap;
   if (s > 256) s = 256;
   if (s < 1) s = 1;
@@ -625,7 +666,7 @@ int splitk_describe(int m, int n, int k, int tile_n, int slices, int flags, int*
   if (!ctx) return st;
   if (m <= 0 || n <= 0 || k <= 0 || slices < 0 || !info) return BEAM_ERR_INVALID_ARG;
   const bool fold = splitk_folds(m, n, tile_n);
-  const int bn = fold ? 128 : splitk_tile_n(n, tile_n);
+  const int bn = fold ? 128 : splitk_pick_tile(m, n, tile_n);
   const int s = splitk_resolve_slices(m, n, k, tile_n, slices, flags);
   const bool one = splitk_one_kernel(ctx, m, n, bn, s, flags, fold);
   info[0] = bn;
@@ -645,7 +686,7 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   DeviceCtx* ctx = current_device_ctx(&st);
   if (!ctx) return st;
   const bool fold = splitk_folds(m, n, tile_n);
-  const int bn = fold ? 128 : splitk_tile_n(n, tile_n);
+  const int bn = fold ? 128 : splitk_pick_tile(m, n, tile_n);
   const int s = splitk_resolve_slices(m, n, k, tile_n, slices, flags);
   const int planes = fold ? 2 * s : s;
   const size_t need = static_cast<size_t>(planes) * m * n * sizeof(float);

@@ -15,6 +15,7 @@ struct GemmPlan {
   int bf16 = 0;       // operands and result are bf16 instead of fp16
   int l2_hints = 0;   // decimal digits: tens = A loads, ones = B loads; 0 normal, 1 evict-first, 2 evict-last
   int ldc = 0;        // row pitch of C in elements (0 = n; a multiple of 8, at least n): C may be a block of columns
+  int whole_tiles = 0;  // 256 x 256 on pairs: 1 = do not cut the last wave's tiles into 128-column halves
   int tiles_in_flight = 0;  // tile_n = 128 only: 0 or 2 = two tiles in flight per CTA (pair), 1 = one tile at a time
 };
 

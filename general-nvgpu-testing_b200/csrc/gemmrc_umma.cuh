@@ -46,6 +46,7 @@ __host__ __device__ constexpr bool is_splitk_mode(int mode) { return mode == kMo
 struct GemmParams {
   CUtensorMap tm_a;  // A  [M, K], box 128 x 64, 128 B swizzle
   CUtensorMap tm_b;  // B  [N, K], box (BN / kCta) x 64, 128 B swizzle
+  CUtensorMap tm_b_tail;  // the same with half as many rows per box, for the half-width tiles of the last wave
   CUtensorMap tm_c;  // C  [M, N] fp16, store box 32 rows x 64 columns, 128 B swizzle
   CUtensorMap tm_s;  // scratch [slices][M][N] fp32, store box 1 x 32 rows x 32 columns, 128 B swizzle
   CUtensorMap tm_peer[7];  // fused all-gather: this rank's row block inside each peer GPU's gathered C
@@ -76,6 +77,7 @@ struct GemmParams {
   int fold;     // split-K of a problem with M, N <= 64: two k-blocks share one 128 x 128 UMMA (see the producer)
   int lead_in;  // two-accumulator tiles: k-blocks issued half-major at the start of a tile (at least 1)
   int lead_out; // ... and at its end
+  int tail_tiles;   // GEMM on CTA pairs, BN = 256: this many tiles at the end of the walk are cut into two 128-column halves
   int rb_granules;  // one-kernel split-K: 32-byte granules of every plane per read-back copy (box of tm_peer[0])
   int* status;  // device fault word
 };
@@ -96,7 +98,11 @@ struct GemmShape {
   static constexpr int kBufsPerWarp = (kMode == kModeLayerNorm) ? 4 : 2;
   static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
-  static constexpr int kThreads = 192;
+  // GEMM with 256 x 256 tiles on pairs has a seventh warp: the second UMMA-issuing thread of a cut tile.
+  // (Even ring depths only: each issuing thread of a cut item takes every other k-block, and with an even depth it
+  // meets a given stage once per pass of the ring, which is what a parity wait can tell apart.)
+  static constexpr bool kCutTiles = kMode == kModeGemm && BN == 256 && kCta == 2 && kStages % 2 == 0;
+  static constexpr int kThreads = kCutTiles ? 256 : 192;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static_assert(BN == 64 || BN == 128 || BN == 256, "UMMA N of the tile");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
@@ -106,6 +112,7 @@ struct GemmShape {
 
 struct WorkItem {
   int mt, nt;        // tile coordinates
+  int half;          // -1: the whole tile; 0 / 1: its left / right half (the cut tiles of the last wave)
   int kb0, kb1;      // k-block range [kb0, kb1)
   int slice;         // split-K slice index
 };
@@ -116,20 +123,31 @@ struct WorkItem {
 //   GEMM, LayerNorm: items are tiles; groups of `group_m` M-tiles are walked N-major so that tiles
 //              in flight together share A rows and B rows in L2 (the reference's CTA remap at
 //              cute_gemm_128x128.cu:23-33, restated for a persistent grid).
+//              With kTail, the last p.tail_tiles tiles of that order are two items each, one per half: when the
+//              tiles do not fill the last wave of a persistent grid by half, halves fill it twice as well and
+//              the wave takes about half as long.
 //   split-K:   items are (tile, slice), slice fastest; k-blocks are dealt out as evenly as possible.
 // How one CTA (pair) walks the work: item j is `first + j * stride`.
 struct Walk {
   int first, stride;
 };
 
-template <int kMode>
+template <int kMode, bool kTail = false>
 __device__ __forceinline__ bool work_item(const GemmParams& p, const Walk& walk, int j, int num_kb, WorkItem& w) {
   const int first = walk.first, stride = walk.stride;
   w.slice = 0;
+  w.half = -1;
   w.kb0 = 0;
   w.kb1 = num_kb;
   if constexpr (!is_splitk_mode(kMode)) {
-    const int t = first + j * stride;
+    int t = first + j * stride;
+    if constexpr (kTail) {
+      const int whole = p.m_tiles * p.n_tiles - p.tail_tiles;  // tiles before the cut ones
+      if (t >= whole) {
+        w.half = (t - whole) & 1;
+        t = whole + ((t - whole) >> 1);
+      }
+    }
     if (t >= p.m_tiles * p.n_tiles) return false;
     const int per_group = p.group_m * p.n_tiles;
     const int g = t / per_group;
@@ -360,7 +378,8 @@ constexpr int kReduceGroups = 8;
 constexpr int kReduceUnitsPerPass = 16;  // float4 output groups that 128 threads (8 groups x 16) reduce together
 
 template <int BN, int kStages, int kCta, int kMode>
-__global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__((GemmShape<BN, kStages, kCta, kMode>::kThreads), 1)
+    gemmrc_umma_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmShape<BN, kStages, kCta, kMode>;
   extern __shared__ uint8_t smem_raw[];
 
@@ -394,6 +413,22 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
   // products (the off-diagonal blocks are ignored).  No shared-memory row is zero fill, and the ring holds twice
   // as much of K.  The two diagonal blocks leave as two partial slices (2 * slice, 2 * slice + 1).
   constexpr bool kCanFold = is_splitk_mode(kMode) && BN == 128 && kCta == 1;
+  // Cut tiles (GEMM on pairs, BN = 256): a pair's LAST item may be one 128-column half of a tile (the launcher cuts at
+  // most one tile per pair).  Its B box has half the rows (tm_b_tail) and its UMMAs have N = 128.  One thread cannot
+  // keep the tensor pipe busy with those (UMMAs into one accumulator complete one after the other, a UMMA of N = 128
+  // is shorter than the gap between two completions, and one thread cannot issue them faster either), nor can one
+  // thread issue a k-block's two copies in the time such a k-block takes.  So a cut item runs on two chains: warp 1
+  // issues the even k-blocks into the left 128 columns of the item's accumulator, warp 6 the odd k-blocks into the
+  // right 128 columns, each releasing the stages it read, and the epilogue adds the two halves; warp 7 issues the
+  // item's B copies while warp 0 issues the A copies.  A cut tile's elements are thus the sum of two partial sums over
+  // alternate k-blocks: a fixed order, but not that of a whole tile.  Warps 6 and 7 sleep on cut_start_bar and
+  // cut_load_bar until warps 1 and 0 reach the cut item: a parity wait on a ring barrier is only meaningful within
+  // one phase of the ring's position, so they must not look at the ring before.  Warp 6 reports the end of its chain
+  // on cut_full_bar.  (The three mbarriers are slots of the LayerNorm mode's landing ring.)
+  constexpr bool kTail = S::kCutTiles;
+  const uint32_t cut_full_bar = bar_base + 8u * (2 * kStages + 4 + 8);
+  const uint32_t cut_start_bar = bar_base + 8u * (2 * kStages + 4 + 9);
+  const uint32_t cut_load_bar = bar_base + 8u * (2 * kStages + 4 + 10);
   const bool fold = kCanFold && p.fold != 0;
   const int num_kb = fold ? ((p.k + S::kBK - 1) / S::kBK + 1) / 2 : (p.k + S::kBK - 1) / S::kBK;
   auto load_stage = [&](int s, int kb, int row_a, int row_b, uint64_t pol_a_, uint64_t pol_b_) {  // one CTA per tile
@@ -422,16 +457,22 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     if constexpr (kMode == kModeLayerNorm) {
       for (uint32_t i = 0; i < 16; ++i) ptx::mbar_init(ln_ring_bar(0) + 8u * i, 1);
     }
+    if constexpr (kTail) {
+      ptx::mbar_init(cut_full_bar, 1);
+      ptx::mbar_init(cut_start_bar, 1);
+      ptx::mbar_init(cut_load_bar, 1);
+    }
     *cta_abort = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
-    if constexpr (is_splitk_mode(kMode)) {
-      // Launched as a programmatic dependent of the previous call's reduction: everything above may run
-      // while that grid drains; nothing below reads or writes global memory before it has completed.
-      // With BEAM_FLAG_INPUTS_STABLE the caller vouches that A and B are not that grid's outputs, and the
+    if constexpr (is_splitk_mode(kMode) || kMode == kModeGemm) {
+      // Launched as a programmatic dependent of the kernel before it on the stream (split-K: the previous call's
+      // reduction): everything above may run while that grid drains; nothing below reads or writes global memory
+      // before it has completed (the other threads pass the CTA barrier below after this wait).
+      // Split-K with BEAM_FLAG_INPUTS_STABLE: the caller vouches that A and B are not that grid's outputs, and the
       // loads below may start at once; the partial stores wait for it in the epilogue either way.
-      if (!(p.flags & 1)) ptx::grid_dependency_wait();
+      if (!is_splitk_mode(kMode) || !(p.flags & 1)) ptx::grid_dependency_wait();
       // In turn, let the next kernel on the stream (this call's reduction kernel, or the next call) become
       // resident early; it blocks in its own griddepcontrol.wait until this grid is done.
       ptx::grid_launch_dependents();
@@ -440,7 +481,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // The ring starts empty, so the first loads need no wait: put them in flight before the CTA-wide
       // set-up barrier (TMEM allocation) instead of after it.  Thread 0 is also the producer thread.
       WorkItem w0;
-      if (work_item<kMode>(p, walk, 0, num_kb, w0)) {
+      if (work_item<kMode, kTail>(p, walk, 0, num_kb, w0)) {
         const int row_a = w0.mt * S::kBM;
         const int row_b = w0.nt * BN;
         for (int kb = w0.kb0; kb < w0.kb1 && preloaded < static_cast<uint32_t>(kStages); ++kb, ++preloaded) {
@@ -468,13 +509,20 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       WorkItem w;
-      for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
+      for (int j = 0; alive && work_item<kMode, kTail>(p, walk, j, num_kb, w); ++j) {
         int row_a = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
-        int row_b = w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
+        const bool cut = kTail && w.half >= 0;
+        int row_b = cut ? w.nt * BN + w.half * (BN / 2) + static_cast<int>(cta_rank) * (S::kBRows / 2)
+                        : w.nt * BN + static_cast<int>(cta_rank) * S::kBRows;
+        const CUtensorMap* map_b = cut ? &p.tm_b_tail : &p.tm_b;
+        const uint32_t pair_bytes = 2u * (S::kABytes + (cut ? S::kBBytes / 2 : S::kBBytes));
         int kb = w.kb0;
         if (j == 0) {  // these are already in flight
           kb += static_cast<int>(preloaded);
           it = preloaded;
+        }
+        if constexpr (kTail) {
+          if (cut) ptx::mbar_arrive(cut_load_bar);  // wake the second producer thread, which loads this item's B boxes
         }
         for (; kb < w.kb1; ++kb, ++it) {
           const int s = it % kStages;
@@ -487,11 +535,36 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             load_stage(s, kb, row_a, row_b, pol_a, pol_b);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), pair_bytes);
             const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
             ptx::tma_load_2d_pair_hint(smem_a(s), &p.tm_a, lead_bar, kb * S::kBK, row_a, pol_a);
-            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b, lead_bar, kb * S::kBK, row_b, pol_b);
+            if (!cut) ptx::tma_load_2d_pair_hint(smem_b(s), map_b, lead_bar, kb * S::kBK, row_b, pol_b);
           }
+        }
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ second TMA producer (cut tiles only)
+    // One thread needs about as long to issue a k-block's two copies as the tensor pipe needs for a whole tile's
+    // k-block, so a cut item, whose k-blocks take half as long, has its B boxes loaded by a thread of their own.
+    if constexpr (kTail) {
+      if (lane == 0) {
+        const uint64_t pol_b = ptx::l2_policy(p.hint_b);
+        WorkItem w;
+        for (int j = 0; work_item<kMode, kTail>(p, walk, j, num_kb, w); ++j) {
+          if (w.half < 0) continue;
+          if (!bounded_wait(cut_load_bar, 0u, cta_abort, p.status, kFaultProducerWait, 30 * kWaitLimitNs)) break;
+          const uint32_t it0 = static_cast<uint32_t>(j) * static_cast<uint32_t>(num_kb);
+          const int row_b = w.nt * BN + w.half * (BN / 2) + static_cast<int>(cta_rank) * (S::kBRows / 2);
+          uint32_t it = it0;
+          for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) break;
+            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b_tail, ptx::mapa(full_bar(s), 0), kb * S::kBK, row_b,
+                                       pol_b);
+          }
+          break;  // a pair has at most one cut item, its last
         }
       }
     }
@@ -499,6 +572,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc_f16_f32(S::kBM * kCta, BN) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
+      const uint32_t idesc_cut = ptx::umma_idesc_f16_f32(S::kBM * kCta, BN / 2) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
       // The issuing thread is a single dependent instruction stream and, for N = 128, has only 256 clocks of tensor
       // work per k-block to hide behind: the stage index and barrier parity advance incrementally (no division), the
       // descriptors are the stage-0 descriptors plus a stride, and a k-block's four UMMAs are one instruction group.
@@ -508,7 +582,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
       bool alive = true;
       WorkItem w;
-      for (int j = 0; alive && work_item<kMode>(p, walk, j, num_kb, w); ++j) {
+      for (int j = 0; alive && work_item<kMode, kTail>(p, walk, j, num_kb, w); ++j) {
         const uint32_t acc = static_cast<uint32_t>(j) & 1u;
         const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
         {
@@ -517,7 +591,19 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        if constexpr (kTail) {
+          if (w.half >= 0) ptx::mbar_arrive(cut_start_bar);  // wake the second issuing thread
+        }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if constexpr (kTail) {
+            if (w.half >= 0 && ((kb - w.kb0) & 1)) {  // the odd k-blocks of a cut item are the second thread's
+              if (++stage == static_cast<uint32_t>(kStages)) {
+                stage = 0;
+                parity ^= 1u;
+              }
+              continue;
+            }
+          }
           {
             const bool landed = bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull);
             if (!landed) {
@@ -526,8 +612,13 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             }
           }
           ptx::tc_fence_after();
-          ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride, idesc,
-                                     kb > w.kb0 ? 1u : 0u);
+          if constexpr (kTail) {
+            ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride,
+                                       w.half >= 0 ? idesc_cut : idesc, kb > w.kb0 ? 1u : 0u);
+          } else {
+            ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride, idesc,
+                                       kb > w.kb0 ? 1u : 0u);
+          }
           if constexpr (kCta == 1)
             ptx::umma_commit<1>(empty_bar(stage));
           else
@@ -542,6 +633,49 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
             ptx::umma_commit<1>(tmem_full_bar(acc));
           else
             ptx::umma_commit_pair_both(tmem_full_bar(acc), 0x3);
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ second MMA issuer (cut tiles only)
+    if constexpr (kTail) {
+      if (lane == 0 && leader) {
+        const uint32_t idesc_cut =
+            ptx::umma_idesc_f16_f32(S::kBM * kCta, BN / 2) | (p.bf16 ? ptx::kIdescBf16Inputs : 0u);
+        const uint64_t a_desc0 = ptx::umma_desc_k_sw128(smem_a(0));
+        const uint64_t b_desc0 = ptx::umma_desc_k_sw128(smem_b(0));
+        constexpr uint64_t kDescStride = static_cast<uint64_t>(S::kStageBytes >> 4);
+        WorkItem w;
+        for (int j = 0; work_item<kMode, kTail>(p, walk, j, num_kb, w); ++j) {
+          if (w.half < 0) continue;
+          // every earlier item was a whole tile of num_kb k-blocks: that fixes the ring position of this one
+          const uint32_t it0 = static_cast<uint32_t>(j) * static_cast<uint32_t>(num_kb);
+          uint32_t stage = it0 % kStages, parity = (it0 / kStages) & 1u;
+          const uint32_t acc = static_cast<uint32_t>(j) & 1u;
+          // Until warp 1 has seen the item's accumulator drained and starts on it.  This wait spans all the whole
+          // tiles before, hence the long limit; an abort anywhere in the CTA still ends it at once.
+          if (!bounded_wait(cut_start_bar, 0u, cta_abort, p.status, kFaultMmaWaitAcc, 30 * kWaitLimitNs)) break;
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN + BN / 2;
+          bool alive = true;
+          for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            if ((kb - w.kb0) & 1) {
+              if (!bounded_wait(full_bar(stage), parity, cta_abort, p.status, kFaultMmaWaitFull)) {
+                alive = false;
+                break;
+              }
+              ptx::tc_fence_after();
+              ptx::umma_f16_kblock<kCta>(d_tmem, a_desc0 + stage * kDescStride, b_desc0 + stage * kDescStride,
+                                         idesc_cut, kb > w.kb0 + 1 ? 1u : 0u);
+              ptx::umma_commit_pair_both(empty_bar(stage), 0x3);
+            }
+            if (++stage == static_cast<uint32_t>(kStages)) {
+              stage = 0;
+              parity ^= 1u;
+            }
+          }
+          if (alive) ptx::umma_commit_pair_both(cut_full_bar, 0x3);
+          break;  // a pair has at most one cut item, its last
         }
       }
     }
@@ -560,7 +694,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
     uint32_t ln_ring_count = 0;                        // LayerNorm: boxes this warp's landing ring has received
     const uint32_t ln_bufs = staging_base + quad * S::kBufsPerWarp * S::kStoreBufBytes;
     WorkItem w;
-    for (int j = 0; work_item<kMode>(p, walk, j, num_kb, w); ++j) {
+    for (int j = 0; work_item<kMode, kTail>(p, walk, j, num_kb, w); ++j) {
       const uint32_t acc = static_cast<uint32_t>(j) & 1u;
       const uint32_t acc_ph = (static_cast<uint32_t>(j) >> 1) & 1u;
       // Lane 0 polls (with back-off) for the whole warp, which stays converged for the .sync.aligned TMEM
@@ -633,11 +767,16 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       } else {
         ready = bounded_wait_warp(tmem_full_bar(acc), acc_ph, cta_abort, p.status, kFaultEpilogueWait, lane);
       }
+      if constexpr (kTail) {
+        if (ready && w.half >= 0)  // the second issuing thread's chain (a pair's only cut item: phase 0)
+          ready = bounded_wait_warp(cut_full_bar, 0u, cta_abort, p.status, kFaultEpilogueWait, lane);
+      }
       if (!ready) break;
       ptx::tc_fence_after();
       const int row0 = w.mt * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;  // first row of this CTA
       const int grow = row0 + static_cast<int>(row_in_tile);
-      const int col0 = w.nt * BN;
+      const bool cut = kTail && w.half >= 0;
+      const int col0 = w.nt * BN + (cut ? w.half * (BN / 2) : 0);
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
       float st_n = 0.f, st_mean = 0.f, st_m2 = 0.f;  // LayerNorm: this row's statistics over this tile
       // One chunk = 128 bytes per row: 64 fp16 columns (GEMM) or 32 fp32 columns (split-K, LayerNorm).
@@ -646,7 +785,7 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
       // Folded split-K: lanes 0..63 own the block in TMEM columns 0..63, lanes 64..127 the one in columns 64..127.
       const int fold_half = fold ? static_cast<int>(quad >> 1) : 0;
       const int c_begin = fold ? fold_half * 64 : 0;
-      const int c_end = fold ? c_begin + 64 : BN;
+      const int c_end = fold ? c_begin + 64 : (cut ? BN / 2 : BN);
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += kChunkCols) {
         uint32_t out[32];  // this row's 128 bytes of the chunk
@@ -655,6 +794,19 @@ __global__ void __launch_bounds__(192, 1) gemmrc_umma_kernel(const __grid_consta
           ptx::tmem_ld_32x32(taddr + c, v0);
           ptx::tmem_ld_32x32(taddr + c + 32, v1);
           ptx::tmem_ld_wait();
+          if constexpr (kTail) {
+            if (cut && w.kb1 - w.kb0 > 1) {  // warp-uniform: add the odd k-blocks' partial sums (the accumulator's other half)
+              uint32_t u[32];
+              ptx::tmem_ld_32x32(taddr + c + BN / 2, u);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 32; ++q) v0[q] = __float_as_uint(__uint_as_float(v0[q]) + __uint_as_float(u[q]));
+              ptx::tmem_ld_32x32(taddr + c + 32 + BN / 2, u);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 32; ++q) v1[q] = __float_as_uint(__uint_as_float(v1[q]) + __uint_as_float(u[q]));
+            }
+          }
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             out[q] = ptx::pack_out2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]), p.bf16);

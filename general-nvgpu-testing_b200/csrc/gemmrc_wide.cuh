@@ -89,6 +89,12 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
     ptx::prefetch_tensormap(&p.tm_c);
+    // Launched as a programmatic dependent of the kernel before it on the stream: this CTA may have become resident
+    // and run the set-up above while that kernel's last CTAs were still at work.  Nothing in this kernel touches
+    // global memory before that grid has completed (every other thread passes the barrier below after this wait).
+    // In turn, the next kernel on the stream may take SMs as this grid's CTAs leave them.
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
   }
   if (warp == 1) {
     ptx::tmem_alloc<2>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);

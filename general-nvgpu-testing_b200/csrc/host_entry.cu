@@ -94,6 +94,7 @@ int run_pipeline(HostPath& h, const void* A_host, const void* B_host, const void
       BEAM_CUDA_TRY(cudaStreamWaitEvent(h.s_mm, h.landed[step], 0), "stream wait");
       GemmPlan plan;
       plan.ldc = n;
+      plan.whole_tiles = 1;  // the copies set the pace here; whole tiles keep every strip's bits those of one whole GEMM
       // the headline tile (256 x 512 per CTA pair) once a strip fills most of a wave of them; 256 x 256 below that
       if (static_cast<long long>((c_rows + 255) / 256) * ((c_cols + 511) / 512) >= 48) plan.tile_n = 512;
       char* devC = static_cast<char*>(h.dC) + static_cast<size_t>(c_r0) * row_c + static_cast<size_t>(c_c0) * 2;

@@ -285,6 +285,30 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                  : "memory");
 }
 // Pair form: the arrive lands on the mbarrier at this offset in every CTA named by cta_mask.
+// Two of a k-block's four K = 16 steps on a CTA pair: the steps whose descriptors lie `first_units` and
+// `first_units + 4` sixteen-byte units into the 128-byte swizzle atom (0 -> steps 0 and 2, 2 -> steps 1 and 3).
+// Two threads, each with an accumulator of its own, share a k-block this way: UMMAs into one accumulator complete one
+// after the other, a UMMA of N = 128 is shorter than the gap between two completions, and one thread cannot issue
+// them faster either; two chains from two threads keep the tensor pipe fed.
+__device__ __forceinline__ void umma_f16_pair_two_steps(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                        uint32_t idesc, uint32_t accumulate_first,
+                                                        uint32_t first_units) {
+  const uint64_t a0 = a_desc + first_units, b0 = b_desc + first_units;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .b64 a, b;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.u64 a, %1, 4;\n\t"
+      "add.u64 b, %2, 4;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, q;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a0), "l"(b0), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+
 // The four UMMAs (K = 16 each) of one 64-wide k-block as a single instruction group: descriptors advance by 32 bytes
 // (two 16-byte units) along K inside the 128-byte swizzle atom; only the first may start a fresh accumulator.
 template <int kCta>

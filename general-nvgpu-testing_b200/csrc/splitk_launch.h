@@ -7,6 +7,8 @@ namespace beam {
 
 // tile_n = 0 picks the tile from N; slices = 0 picks the split factor from the SM count.
 int splitk_tile_n(int n, int tile_n);
+// ... and from M and N: the 256-wide tile for problems with more arithmetic than memory time (see gemmrc_launch.cu).
+int splitk_pick_tile(int m, int n, int tile_n);
 bool splitk_folds(int m, int n, int tile_n);
 int splitk_heuristic(int m, int n, int k, int tile_n, int flags = 0);
 int splitk_resolve_slices(int m, int n, int k, int tile_n, int requested, int flags = 0);

@@ -82,6 +82,14 @@ typedef struct beam_gemm_cfg {
 /* Split-K only.  Run the call as one kernel wherever that form applies, including calls that carry
  * BEAM_FLAG_INPUTS_STABLE (which run as two kernels by default). */
 #define BEAM_FLAG_SPLITK_ONE_KERNEL 8
+/* beam_gemmrc_fp16 with 256 x 256 tiles on CTA pairs only.  By default, when the tiles of the persistent grid's last
+ * wave occupy at most half of the CTA pairs, each of them is computed as two 128-column halves by two pairs, and a
+ * half tile adds up the even and the odd 64-wide blocks of K separately before adding the two sums (two UMMA chains
+ * keep the tensor pipe busy where one chain of N = 128 instructions cannot).  The order is fixed, so results are
+ * reproducible run to run, but an element of a cut tile can differ in its last bit from the same element computed in
+ * a whole tile.  This flag keeps every tile whole: one summation order everywhere, for comparison and for callers
+ * that compare bits across different shapes. */
+#define BEAM_FLAG_WHOLE_TILES 16
 
 BEAM_API const char* beam_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */

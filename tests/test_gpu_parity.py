@@ -123,6 +123,38 @@ def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     _healthy(beam)
 
 
+def test_cut_tiles_of_the_last_wave(beam, oracle_mod):
+    """256 x 256 tiles on CTA pairs: when the last wave of the persistent grid would occupy at most half of the pairs,
+    its tiles are computed as 128-column halves on two UMMA chains (even and odd k-blocks summed separately).  A
+    4096 x 4096 problem has 256 tiles, three waves of 74 pairs and 34 tiles over: whole and cut tiles in one launch.
+    The result must match the oracle, repeat bit for bit, and stay within rounding of the all-whole-tiles result;
+    with one k-block, or a ring depth that does not support cutting, the two forms are the same bits."""
+    m, n, k = 4096, 4096, 192
+    a, b = _inputs(m, n, k, 0.1, 4242)
+    da, db = _dev(a), _dev(b)
+    want = oracle_mod.gemmrc(a, b)
+    cut = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.gemmrc(da, db, cut, tile_n=256, cta_pair=2)
+    assert oracle_mod.floored_max_rel(cut.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    again = torch.zeros_like(cut)
+    beam.gemmrc(da, db, again, tile_n=256, cta_pair=2)
+    assert torch.equal(cut, again)
+    whole = torch.zeros_like(cut)
+    beam.gemmrc(da, db, whole, tile_n=256, cta_pair=2, whole_tiles=True)
+    assert oracle_mod.floored_max_rel(whole.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    assert oracle_mod.floored_max_rel(cut.cpu().numpy(), whole.cpu().numpy()) <= 2e-3
+    odd_ring = torch.zeros_like(cut)
+    beam.gemmrc(da, db, odd_ring, tile_n=256, cta_pair=2, stages=5)  # no cutting with an odd ring depth
+    assert torch.equal(odd_ring, whole)
+    one_kb = torch.zeros(512, 512, dtype=torch.float16, device="cuda")
+    one_kb_whole = torch.zeros_like(one_kb)
+    beam.gemmrc(da[:512, :64].contiguous(), db[:512, :64].contiguous(), one_kb, tile_n=256, cta_pair=2)
+    beam.gemmrc(da[:512, :64].contiguous(), db[:512, :64].contiguous(), one_kb_whole, tile_n=256, cta_pair=2,
+                whole_tiles=True)
+    assert torch.equal(one_kb, one_kb_whole)
+    _healthy(beam)
+
+
 def test_random_shapes_all_paths(beam, oracle_mod):
     """Seeded sweep of awkward shapes through the large-GEMM tile families, split-K and the fused LayerNorm."""
     rng = np.random.Generator(np.random.PCG64(2024))
@@ -182,7 +214,8 @@ def test_zero_and_identity_inputs(beam):
 
 def test_permutation_and_scaling_properties(beam, oracle_mod):
     """Size-independent properties: permuting the rows of A (columns of C come from rows of B) permutes C bit
-    for bit, because every output is the same dot product wherever its tile lands; and (2A) B^T equals
+    for bit, because every output is the same dot product wherever its tile lands (all six tiles of this problem are
+    computed the same way); and (2A) B^T equals
     2 (A B^T) to rounding (not bitwise: the tensor cores need not treat subnormal fp16 inputs like normals)."""
     a, b = _inputs(640, 512, 1024, 0.1, 77)
     da, db = _dev(a), _dev(b)
@@ -454,7 +487,7 @@ def test_host_buffer_entry_strips(beam, oracle_mod, m, n, k):
     beam.gemmrc_host(pa, pb, pc)
     assert oracle_mod.floored_max_rel(pc.numpy(), want) <= oracle_mod.REL_TOL
     dc = torch.zeros(m, n, dtype=torch.float16, device="cuda")
-    beam.cutlass_gemmrc(pa.cuda(), pb.cuda(), dc)
+    beam.gemmrc(pa.cuda(), pb.cuda(), dc, whole_tiles=True)  # the host entry multiplies whole tiles only
     assert torch.equal(dc.cpu(), pc), "host-buffer path and device path must agree bit for bit"
     pc2 = torch.full((m, n), 7.0, dtype=torch.float16).pin_memory()
     beam.gemmrc_host_rows(pa, pb.cuda(), pc2)
