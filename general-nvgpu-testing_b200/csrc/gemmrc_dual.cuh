@@ -35,7 +35,7 @@ struct DualShape {
   static constexpr int kBufsPerWarp = 2;
   static constexpr int kStagingBytes = 4 * kBufsPerWarp * kStoreBufBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;
-  static constexpr int kThreads = 224;  // producer, first issuer, four epilogue warps, second issuer
+  static constexpr int kThreads = 256;  // producer (A boxes), first issuer, four epilogue warps, second issuer, producer (B box)
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static_assert((2 * kStages + 4) * 8 + 32 <= kBarBytes, "barrier block too small");
   static_assert(kABytes % 1024 == 0 && kBBytes % 1024 == 0, "boxes must keep the 1024-byte alignment of the swizzle atom");
@@ -53,7 +53,7 @@ __device__ __forceinline__ void dual_item_coords(const GemmParams& p, int t, int
 }
 
 template <int kStages, int kCta>
-__global__ void __launch_bounds__(224, 1) gemmrc_dual_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__((DualShape<kStages, kCta>::kThreads), 1) gemmrc_dual_kernel(const __grid_constant__ GemmParams p) {
   using S = DualShape<kStages, kCta>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5;
@@ -115,13 +115,11 @@ __global__ void __launch_bounds__(224, 1) gemmrc_dual_kernel(const __grid_consta
       uint32_t it = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
-      const uint64_t pol_b = ptx::l2_policy(p.hint_b);
       for (int j = 0; alive && first + j * stride < items; ++j) {
         int mt2, nt;
         dual_item_coords(p, first + j * stride, mt2, nt);
         int row_a[2];
         for (int h = 0; h < 2; ++h) row_a[h] = (2 * mt2 + h) * (S::kBM * kCta) + static_cast<int>(cta_rank) * S::kBM;
-        const int row_b = nt * S::kBN + static_cast<int>(cta_rank) * S::kBRows;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -133,15 +131,40 @@ __global__ void __launch_bounds__(224, 1) gemmrc_dual_kernel(const __grid_consta
             ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
             for (int h = 0; h < 2; ++h)
               ptx::tma_load_2d_hint(smem_a(s, h), &p.tm_a, full_bar(s), kb * S::kBK, row_a[h], pol_a);
-            ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
             const uint32_t lead_bar = ptx::mapa(full_bar(s), 0);
             for (int h = 0; h < 2; ++h)
               ptx::tma_load_2d_pair_hint(smem_a(s, h), &p.tm_a, lead_bar, kb * S::kBK, row_a[h], pol_a);
-            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b, lead_bar, kb * S::kBK, row_b, pol_b);
           }
+        }
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ second TMA producer: the B boxes
+    // One thread issuing all three copies of a k-block cannot quite keep up with the two tiles' UMMAs at full clocks;
+    // with the B box on a thread of its own the kernel gains 1.7 % (one CTA per tile) and 3.5 % (pairs) at 8192^3
+    // (a thread per box is slower again).  Both producers walk the same items and wait on the same empty barriers.
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      const uint64_t pol_b = ptx::l2_policy(p.hint_b);
+      for (int j = 0; alive && first + j * stride < items; ++j) {
+        int mt2, nt;
+        dual_item_coords(p, first + j * stride, mt2, nt);
+        const int row_b = nt * S::kBN + static_cast<int>(cta_rank) * S::kBRows;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!bounded_wait(empty_bar(s), ph ^ 1u, cta_abort, p.status, kFaultProducerWait)) {
+            alive = false;
+            break;
+          }
+          if constexpr (kCta == 1)
+            ptx::tma_load_2d_hint(smem_b(s), &p.tm_b, full_bar(s), kb * S::kBK, row_b, pol_b);
+          else
+            ptx::tma_load_2d_pair_hint(smem_b(s), &p.tm_b, ptx::mapa(full_bar(s), 0), kb * S::kBK, row_b, pol_b);
         }
       }
     }
