@@ -671,6 +671,18 @@ def run_profile_case(args):
               "gemm128x128_single": lambda: beam.gemmrc(a, b, c, tile_n=128, cta_pair=1, tiles_in_flight=1),
               "gemm256x128_single": lambda: beam.gemmrc(a, b, c, tile_n=128, cta_pair=2, tiles_in_flight=1),
               "gemm": lambda: beam.cutlass_gemmrc(a, b, c)}[args.profile]
+    elif args.profile in ("gemm256_lastwave_4096", "gemm256_lastwave_1024"):
+        # 256 x 256 tiles on pairs at a size whose last wave fills at most half of the pairs: launches alternate
+        # between whole tiles and the default (last-wave tiles cut into halves), whole first
+        m, n, k = (4096, 4096, 4096) if args.profile.endswith("4096") else (1024, 1024, 8192)
+        a = (torch.randn(m, k, device="cuda") * 0.1).half()
+        b = (torch.randn(n, k, device="cuda") * 0.1).half()
+        c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        turn = [0]
+
+        def fn():
+            beam.gemmrc(a, b, c, tile_n=256, cta_pair=2, whole_tiles=(turn[0] % 2 == 0))
+            turn[0] += 1
     elif args.profile in ("splitk", "splitk64", "splitk_plain", "splitk64_plain"):
         m, n, k = (128, 256, 65536) if args.profile.startswith("splitk_") or args.profile == "splitk" else (64, 64, 131072)
         a = (torch.rand(m, k, device="cuda") * 2 - 1).half()
@@ -704,7 +716,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the cuBLAS / split-K / LayerNorm side measurements")
     ap.add_argument("--profile", default=None,
                     choices=["gemm", "gemm256", "gemm128x128", "gemm256x128", "gemm128x128_single", "gemm256x128_single",
-                             "cublas", "splitk", "splitk64", "splitk_plain", "splitk64_plain", "layernorm"],
+                             "cublas", "splitk", "splitk64", "splitk_plain", "splitk64_plain", "layernorm",
+                             "gemm256_lastwave_4096", "gemm256_lastwave_1024"],
                     help="run a few launches of one kernel and exit (the command the ncu captures in profiles/ wrap)")
     args = ap.parse_args()
     if args.profile:

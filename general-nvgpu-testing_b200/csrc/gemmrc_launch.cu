@@ -719,8 +719,12 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
 
   // Fixed-order reduction, launched so that its blocks may become resident while the partial
   // kernel drains; it blocks in griddepcontrol.wait until every partial is written and visible.
+  // Small outputs: a block per row x 128 columns, the eight groups of planes summed by eight warps side by side (the
+  // shortest chain of dependent loads).  From 64 Ki outputs on: one thread per four columns (one wave of blocks).
+  const bool flat = static_cast<long long>(m) * n >= 65536;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((n + 127) / 128), static_cast<unsigned>(m), 1);
+  cfg.gridDim = flat ? dim3(static_cast<unsigned>((static_cast<long long>(m) * (n / 4) + 255) / 256), 1, 1)
+                     : dim3(static_cast<unsigned>((n + 127) / 128), static_cast<unsigned>(m), 1);
   cfg.blockDim = dim3(256, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
@@ -729,8 +733,8 @@ int launch_splitk(const void* A, const void* B, void* C, int m, int n, int k, in
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float*>(workspace),
-                                   static_cast<__half*>(C), m, n, planes),
+  BEAM_CUDA_TRY(cudaLaunchKernelEx(&cfg, flat ? splitk_reduce_flat_kernel : splitk_reduce_kernel,
+                                   static_cast<const float*>(workspace), static_cast<__half*>(C), m, n, planes),
                 "cudaLaunchKernelEx(splitk_reduce)");
   return BEAM_OK;
 }

@@ -975,4 +975,56 @@ static __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* 
   }
 }
 
+
+// The same sum for larger outputs (a split-K problem of 512 x 512 and up): one thread per 4 columns walks all the
+// planes, eight loads in flight, and folds a group's sum into the total when the walk leaves the group, so the
+// additions are those of splitk_reduce_kernel in the same order (bit-identical), without its block per row and
+// its exchange through shared memory: with a million outputs that kernel needs seven waves of short blocks.
+static __global__ void __launch_bounds__(256) splitk_reduce_flat_kernel(const float* __restrict__ partial,
+                                                                        __half* __restrict__ c, int m, int n,
+                                                                        int slices) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
+  const int quads = n >> 2;  // N is a multiple of 8
+  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= static_cast<long long>(m) * quads) return;
+  const int row = static_cast<int>(idx / quads);
+  const int col = static_cast<int>(idx - static_cast<long long>(row) * quads) * 4;
+  const size_t plane = static_cast<size_t>(m) * n;
+  const float* src = partial + static_cast<size_t>(row) * n + col;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), t = acc;
+  int g = 0;
+  int g_end = slices / kReduceGroups;  // slices * (g + 1) / kReduceGroups for g = 0
+  auto fold = [&]() {
+    if (g == 0) {
+      t = acc;
+    } else {
+      t.x += acc.x; t.y += acc.y; t.z += acc.z; t.w += acc.w;
+    }
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    ++g;
+    g_end = slices * (g + 1) / kReduceGroups;
+  };
+  constexpr int kBatch = 8;
+  for (int s = 0; s < slices; s += kBatch) {
+    float4 v[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      v[i] = (s + i < slices) ? __ldcg(reinterpret_cast<const float4*>(src + plane * (s + i)))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      if (s + i < slices) {
+        while (s + i >= g_end) fold();  // the walk has left group g (groups may be empty)
+        acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w;
+      }
+    }
+  }
+  while (g < kReduceGroups) fold();
+  uint2 o;
+  o.x = ptx::pack_half2(t.x, t.y);
+  o.y = ptx::pack_half2(t.z, t.w);
+  *reinterpret_cast<uint2*>(c + static_cast<size_t>(row) * n + col) = o;
+}
+
 }  // namespace beam

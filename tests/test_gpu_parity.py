@@ -303,7 +303,8 @@ def test_config3_splitk(beam, oracle_mod, m, n, k, tile_n, slices):
 
 
 @pytest.mark.parametrize("m,n,k,tile_n,slices", [(128, 256, 16384, 128, 32), (64, 64, 32768, 64, 0),
-                                                 (72, 200, 4096, 64, 7)])
+                                                 (72, 200, 4096, 64, 7), (512, 512, 4096, 256, 0),
+                                                 (520, 264, 2048, 128, 5)])
 def test_splitk_exact_on_integer_inputs(beam, oracle_mod, m, n, k, tile_n, slices):
     """With small integer inputs every product and every partial sum is exact in fp32, so the order of the
     additions does not matter and the kernel must reproduce the slice-ordered CPU restatement bit for bit."""
@@ -331,6 +332,26 @@ def test_splitk_default_entry(beam, oracle_mod):
         c.zero_()
         beam.cutlass_gemmrc_splitk(a=_dev(a), b=_dev(b), c=c, split_k_slices=s)
         assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 8192), (1024, 1024, 2048), (520, 264, 4104), (300, 1000, 1096)])
+def test_splitk_medium_shapes(beam, oracle_mod, m, n, k):
+    """Split-K beyond the small-M-N shapes (512 x 512 x 8192 is the reference's own split-K test call,
+    python/gemm_test.py:201): problems with more arithmetic than memory time take the 256-wide tile and a slice per SM,
+    and outputs of 64 Ki elements and more are summed by the one-thread-per-four-columns reduction.  Against the
+    oracle, and twice for the same bits."""
+    a, b = _inputs(m, n, k, "uniform", 7 * m + n + k)
+    want = oracle_mod.gemmrc(a, b)
+    plan = beam.splitk_describe(m, n, k)
+    if m * n >= 200 * (m + n) and n >= 256:
+        assert plan["tile_n"] == 256 and plan["slices"] >= 1
+    c = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    beam.cutlass_gemmrc_splitk(_dev(a), _dev(b), c)
+    assert oracle_mod.floored_max_rel(c.cpu().numpy(), want) <= oracle_mod.REL_TOL
+    again = torch.full_like(c, 5.0)
+    beam.cutlass_gemmrc_splitk(_dev(a), _dev(b), again)
+    assert torch.equal(c, again)
+    _healthy(beam)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (300, 1000, 264), (512, 4096, 512), (96, 264, 320)])
