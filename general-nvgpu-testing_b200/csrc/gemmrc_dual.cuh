@@ -94,9 +94,9 @@ __global__ void __launch_bounds__((DualShape<kStages, kCta>::kThreads), 1) gemmr
     ptx::prefetch_tensormap(&p.tm_a);
     ptx::prefetch_tensormap(&p.tm_b);
     ptx::prefetch_tensormap(&p.tm_c);
-    // A programmatic dependent of the kernel before it on the stream: the set-up above may overlap that kernel's last
-    // CTAs; no thread touches global memory before that grid has completed (the barrier below follows this wait).
-    ptx::grid_dependency_wait();
+    // A programmatic dependent of the kernel before it on the stream: the whole set-up may overlap that kernel's last
+    // CTAs; the two producer threads wait for that grid before their first load, and nothing is written before data
+    // has arrived.
     ptx::grid_launch_dependents();
   }
   if (warp == 1) {
@@ -112,6 +112,7 @@ __global__ void __launch_bounds__((DualShape<kStages, kCta>::kThreads), 1) gemmr
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      ptx::grid_dependency_wait();
       uint32_t it = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
@@ -147,6 +148,7 @@ __global__ void __launch_bounds__((DualShape<kStages, kCta>::kThreads), 1) gemmr
     // with the B box on a thread of its own the kernel gains 1.7 % (one CTA per tile) and 3.5 % (pairs) at 8192^3
     // (a thread per box is slower again).  Both producers walk the same items and wait on the same empty barriers.
     if (lane == 0) {
+      ptx::grid_dependency_wait();
       uint32_t it = 0;
       bool alive = true;
       const uint64_t pol_b = ptx::l2_policy(p.hint_b);
@@ -273,7 +275,12 @@ __global__ void __launch_bounds__((DualShape<kStages, kCta>::kThreads), 1) gemmr
     }
   }
 
-  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+  if (warp >= 2 && lane == 0) {  // staging buffers read; stores into peer GPUs are waited for in full
+    if (p.n_peers == 0)
+      ptx::tma_store_wait_read<0>();
+    else
+      ptx::tma_store_wait_all<0>();
+  }
   __syncwarp();
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();

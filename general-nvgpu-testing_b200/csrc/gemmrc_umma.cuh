@@ -472,7 +472,9 @@ __global__ void __launch_bounds__((GemmShape<BN, kStages, kCta, kMode>::kThreads
       // before it has completed (the other threads pass the CTA barrier below after this wait).
       // Split-K with BEAM_FLAG_INPUTS_STABLE: the caller vouches that A and B are not that grid's outputs, and the
       // loads below may start at once; the partial stores wait for it in the epilogue either way.
-      if (!is_splitk_mode(kMode) || !(p.flags & 1)) ptx::grid_dependency_wait();
+      // (GEMM on pairs: only the producer threads read global memory before anything is written, and they wait
+      // after the set-up barriers below instead, which then overlap the preceding grid's tail as well.)
+      if (is_splitk_mode(kMode) ? !(p.flags & 1) : kCta == 1) ptx::grid_dependency_wait();
       // In turn, let the next kernel on the stream (this call's reduction kernel, or the next call) become
       // resident early; it blocks in its own griddepcontrol.wait until this grid is done.
       ptx::grid_launch_dependents();
@@ -504,6 +506,7 @@ __global__ void __launch_bounds__((GemmShape<BN, kStages, kCta, kMode>::kThreads
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      if constexpr (kMode == kModeGemm && kCta == 2) ptx::grid_dependency_wait();  // before the first global read
       uint32_t it = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
@@ -912,7 +915,14 @@ __global__ void __launch_bounds__((GemmShape<BN, kStages, kCta, kMode>::kThreads
 
   // ---- teardown: bulk stores must have finished reading shared memory (and, for the kernels that follow,
   // writing global memory) before the CTA goes away; then everyone meets and the allocating warp frees TMEM
-  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+  if (warp >= 2 && lane == 0) {
+    // A plain GEMM only needs its staging buffers back (the stores have READ them); their writes to C complete with
+    // the grid like any other store.  Partials, LayerNorm panels and stores into peer GPUs are waited for in full.
+    if (kMode == kModeGemm && p.n_peers == 0)
+      ptx::tma_store_wait_read<0>();
+    else
+      ptx::tma_store_wait_all<0>();
+  }
   __syncwarp();
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();

@@ -90,10 +90,9 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     ptx::prefetch_tensormap(&p.tm_b);
     ptx::prefetch_tensormap(&p.tm_c);
     // Launched as a programmatic dependent of the kernel before it on the stream: this CTA may have become resident
-    // and run the set-up above while that kernel's last CTAs were still at work.  Nothing in this kernel touches
-    // global memory before that grid has completed (every other thread passes the barrier below after this wait).
+    // and run the set-up (this block, the TMEM allocation, the barriers below) while that kernel's last CTAs were still
+    // at work.  The producer thread waits for that grid before its first load; nothing is written before data arrives.
     // In turn, the next kernel on the stream may take SMs as this grid's CTAs leave them.
-    ptx::grid_dependency_wait();
     ptx::grid_launch_dependents();
   }
   if (warp == 1) {
@@ -110,6 +109,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
+      ptx::grid_dependency_wait();  // the preceding grid has completed: A and B may be its outputs
       uint32_t it = 0;
       bool alive = true;
       const uint64_t pol_a = ptx::l2_policy(p.hint_a);
@@ -324,7 +324,12 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
     }
   }
 
-  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+  if (warp >= 2 && lane == 0) {  // staging buffers read; stores into peer GPUs are waited for in full
+    if (p.n_peers == 0)
+      ptx::tma_store_wait_read<0>();
+    else
+      ptx::tma_store_wait_all<0>();
+  }
   __syncwarp();
   if (*cta_abort) abort_drain_delay();
   ptx::tc_fence_before();

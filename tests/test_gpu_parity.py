@@ -123,6 +123,37 @@ def test_ragged_shapes(beam, oracle_mod, m, n, k, tile_n, cta_pair):
     _healthy(beam)
 
 
+@pytest.mark.parametrize("knobs", [dict(tile_n=256, cta_pair=2), dict(tile_n=512, cta_pair=2), dict(tile_n=128, cta_pair=1),
+                                   dict(tile_n=128, cta_pair=2), dict(tile_n=256, cta_pair=1)])
+def test_dependent_launches_see_their_predecessors_output(beam, knobs):
+    """Every large-GEMM kernel is a programmatic dependent launch: it sets itself up while the kernel before it on the
+    stream drains and waits for that kernel's completion before its first load.  A chain in which each GEMM multiplies
+    the previous GEMM's output (written with bulk stores that the writing kernel does not wait out) must give the bits
+    of the same chain run with a device-wide synchronisation after every launch."""
+    torch.manual_seed(5)
+    m, n = 1536, 1536
+    x0 = (torch.randn(m, n, device="cuda") * 0.05).half()
+    ws = [(torch.randn(n, n, device="cuda") * n ** -0.5).half() for _ in range(3)]  # keeps the chain's magnitude
+
+    def chain(sync):
+        bufs = [torch.zeros(m, n, dtype=torch.float16, device="cuda") for _ in range(2)]
+        src = x0
+        for i in range(24):
+            dst = bufs[i % 2]
+            beam.gemmrc(src, ws[i % 3], dst, **knobs)
+            if sync:
+                torch.cuda.synchronize()
+            src = dst
+        torch.cuda.synchronize()
+        return src.clone()
+
+    want = chain(True)
+    for _ in range(3):
+        assert torch.equal(chain(False), want)
+    assert torch.isfinite(want.float()).all() and want.float().abs().max() > 0
+    _healthy(beam)
+
+
 def test_cut_tiles_of_the_last_wave(beam, oracle_mod):
     """256 x 256 tiles on CTA pairs: when the last wave of the persistent grid would occupy at most half of the pairs,
     its tiles are computed as 128-column halves on two UMMA chains (even and odd k-blocks summed separately).  A
