@@ -488,7 +488,6 @@ static int launch_gemmrc_ex(const void* A, const void* B, void* C, int m, int n,
       return launch_dual_instance<4, 2>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
     return launch_dual_instance<4, 1>(ctx, A, B, C, m, n, k, plan.group_m, plan.max_ctas, ex, stream);
   }
-  BEAM_GEMM_CASE(256, 3, 2)
   BEAM_GEMM_CASE(256, 4, 2)
   BEAM_GEMM_CASE(256, 5, 2)
   BEAM_GEMM_CASE(256, 6, 2)
