@@ -146,8 +146,9 @@ int launch_instance(DeviceCtx* ctx, const void* A, const void* B, void* C, int m
   if (max_ctas > 0 && max_ctas / kCta < clusters) clusters = max_ctas / kCta > 0 ? max_ctas / kCta : 1;
   if (S::kCutTiles) {
     // The last wave of the persistent grid: when its tiles occupy at most half of the pairs, they are cut into
-    // 128-column halves, which occupy twice as many pairs for about half as long (4096^3: 256 tiles on 74 pairs are
-    // 3 waves and 34 tiles; as 68 halves those take 0.6 of a wave instead of a whole one).
+    // 128-column halves, which occupy twice as many pairs for a shorter time (4096^3: 256 tiles on 74 pairs are
+    // 3 waves and 34 tiles; as 68 halves those take 0.77 of a wave instead of a whole one, measured).  At most one
+    // cut item per pair, and it is the pair's last: the kernel relies on both.
     st = encode_tmap_2d(&p.tm_b_tail, B, 2, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
                         static_cast<uint64_t>(k), S::kBRows / 2, S::kBK, true);
     if (st != BEAM_OK) return st;

@@ -19,7 +19,12 @@
 // CTAs' shared memory and writes both CTAs' TMEM, and completion is fanned out to both CTAs with
 // the two-CTA form of tcgen05.commit.
 //
-// Three epilogues share this pipeline:
+// GEMM mode with 256 x 256 tiles on pairs runs two more warps (6: a second MMA issuer, 7: a second producer), idle
+// except in a pair's last item when the launcher has cut the tiles of the last wave into halves (see kTail below).
+// All GEMM-mode launches are programmatic dependents of the kernel before them on the stream: set-up overlaps that
+// kernel's tail, the producer waits for its completion before the first load.
+//
+// Four epilogues share this pipeline:
 //   kModeGemm       fp32 -> fp16, store C.
 //   kModeSplitK     a work item is (tile, K slice); the fp32 partial goes to workspace[slice][M][N]
 //                   and a second kernel sums the slices in index order.
