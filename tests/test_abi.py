@@ -106,6 +106,12 @@ def test_splitk_sizing_functions(lib):
     assert h(64, 64, 256, 64) == 1                        # too little K to split
     # a split factor beyond K/64 falls back to the heuristic
     assert ws(64, 64, 128, 64, 50) == 2 * h(64, 64, 128, 64) * 64 * 64 * 4
+    # medium M, N with more arithmetic than memory time (M N / (M + N) >= 200): the 256-wide tile, a slice per SM,
+    # at least 8 k-blocks per slice (148 SMs assumed without a device)
+    assert h(512, 512, 8192, 0) == 16                     # 8 tiles of 128 x 256: 148 / 8 = 18, capped by 128 k-blocks / 8
+    assert h(1024, 1024, 8192, 0) == 4                    # 32 tiles: 148 / 32
+    assert ws(512, 512, 8192, 0, 0) == 16 * 512 * 512 * 4
+    assert h(128, 256, 65536, 0) == h(128, 256, 65536, 128)   # the HBM-bound shapes keep the 128-wide tile
     ln = lib.beam_gemmrc_layernorm_workspace_bytes
     ln.restype = ctypes.c_size_t
     ln.argtypes = [i, i, i]
