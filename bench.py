@@ -659,9 +659,11 @@ def run_profile_case(args):
     torch.manual_seed(SEED)
     n_launch = max(args.steps, 1)
     if args.profile in ("gemm", "gemm256", "gemm128x128", "gemm256x128", "gemm128x128_single", "gemm256x128_single",
-                        "cublas"):  # cublas: the comparison kernel on the same inputs
-        a = (torch.randn(M_PER_GPU, K, device="cuda") * 0.1).half()
-        b = (torch.randn(N, K, device="cuda") * 0.1).half()
+                        "cublas", "gemm_k4096", "gemm256_k4096", "cublas_k4096"):  # cublas: the comparison kernel
+        k_dim = 4096 if args.profile.endswith("_k4096") else K  # "_k4096": the same output with half the K
+        args.profile = args.profile.replace("_k4096", "")
+        a = (torch.randn(M_PER_GPU, k_dim, device="cuda") * 0.1).half()
+        b = (torch.randn(N, k_dim, device="cuda") * 0.1).half()
         c = torch.zeros(M_PER_GPU, N, dtype=torch.float16, device="cuda")
         fn = {"cublas": lambda: beam.cublas_gemmexrc(a, b, c),
               "gemm256": lambda: beam.cutlass_gemmrc_spec(a, b, c, shape_threadblock=[256, 256]),  # one accumulator per tile
@@ -717,7 +719,8 @@ def main():
     ap.add_argument("--profile", default=None,
                     choices=["gemm", "gemm256", "gemm128x128", "gemm256x128", "gemm128x128_single", "gemm256x128_single",
                              "cublas", "splitk", "splitk64", "splitk_plain", "splitk64_plain", "layernorm",
-                             "gemm256_lastwave_4096", "gemm256_lastwave_1024"],
+                             "gemm256_lastwave_4096", "gemm256_lastwave_1024", "gemm_k4096", "gemm256_k4096",
+                             "cublas_k4096"],
                     help="run a few launches of one kernel and exit (the command the ncu captures in profiles/ wrap)")
     args = ap.parse_args()
     if args.profile:

@@ -82,9 +82,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Arrive on an mbarrier that may live in another CTA of the cluster (address from mapa()).
+// Arrive on an mbarrier that may live in another CTA of the cluster (address from mapa()).  Used to hand a TMEM
+// accumulator back to the issuing thread: what must be ordered before the arrive are this thread's tcgen05.ld
+// (tcgen05.wait::ld and tcgen05.fence::before_thread_sync do that), not writes to memory, so the arrive carries the
+// default release at CTA scope.  With .release.cluster the arriving thread stalled for about 1.5 us per hand-back
+// (time stamps: the issuing thread saw the accumulator back 1.7 us after the last epilogue warp had it in registers).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
