@@ -263,16 +263,16 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       // Both halves are handed back as soon as their accumulators sit in registers, before anything is rounded or
       // stored: the issuer's wait then depends on TMEM load latency only, not on how fast the (bursty, all CTAs at
       // once) C stores drain the staging buffers.
-      uint32_t va0[32], va1[32], vb0[32], vb1[32], out[32];
+      uint32_t va0[32], va1[32], vb0[32], vb1[32], out[32], out_b[32];
       auto load_chunk = [&](int i, uint32_t (&lo)[32], uint32_t (&hi)[32]) {
         ptx::tmem_ld_32x32(lane_base + chunk_col(i), lo);
         ptx::tmem_ld_32x32(lane_base + chunk_col(i) + 32, hi);
       };
-      auto round_chunk = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32]) {
+      auto round_chunk = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], uint32_t (&dst)[32]) {
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          out[q] = ptx::pack_out2(__uint_as_float(lo[2 * q]), __uint_as_float(lo[2 * q + 1]), p.bf16);
-          out[16 + q] = ptx::pack_out2(__uint_as_float(hi[2 * q]), __uint_as_float(hi[2 * q + 1]), p.bf16);
+          dst[q] = ptx::pack_out2(__uint_as_float(lo[2 * q]), __uint_as_float(lo[2 * q + 1]), p.bf16);
+          dst[16 + q] = ptx::pack_out2(__uint_as_float(hi[2 * q]), __uint_as_float(hi[2 * q + 1]), p.bf16);
         }
       };
       auto release_half = [&](uint32_t h) {
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(lead_empty0 + 8u * h);
       };
-      auto stage_and_store = [&](int i) {
+      auto stage_and_store = [&](int i, const uint32_t (&src)[32]) {
         const int col = tile_col0 + out_col(i);
         const int row = row0 + out_row(i);
         if (col < p.n && row < p.m) {
@@ -293,8 +293,8 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
           const uint32_t row_addr = buf + lane * 128u;
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj)
-            ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), out[4 * jj],
-                              out[4 * jj + 1], out[4 * jj + 2], out[4 * jj + 3]);
+            ptx::st_shared_v4(row_addr + ((static_cast<uint32_t>(jj) ^ (lane & 7u)) << 4), src[4 * jj],
+                              src[4 * jj + 1], src[4 * jj + 2], src[4 * jj + 3]);
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) store_c_box(p, buf, col, row);
@@ -305,22 +305,24 @@ __global__ void __launch_bounds__(WideShape<kStages>::kThreads, 1) gemmrc_wide_k
       load_chunk(1, vb0, vb1);
       ptx::tmem_ld_wait();
       release_half(0);
-      round_chunk(va0, va1);
+      // Half 1 completes two half-k-blocks after half 0: that time goes into rounding half 0 and storing its first
+      // chunk, so that once half 1 is complete nothing but its TMEM loads stands between it and its hand-back.
+      round_chunk(va0, va1, out);
+      stage_and_store(0, out);
+      round_chunk(vb0, vb1, out_b);
       if (!bounded_wait_warp(tmem_full_bar(1), static_cast<uint32_t>(j) & 1u, cta_abort, p.status,
                              kFaultEpilogueWait, lane))
         break;
       ptx::tc_fence_after();
       load_chunk(2, va0, va1);
-      stage_and_store(0);
-      round_chunk(vb0, vb1);
       load_chunk(3, vb0, vb1);
       ptx::tmem_ld_wait();
       release_half(1);
-      stage_and_store(1);
-      round_chunk(va0, va1);
-      stage_and_store(2);
-      round_chunk(vb0, vb1);
-      stage_and_store(3);
+      stage_and_store(1, out_b);
+      round_chunk(va0, va1, out);
+      stage_and_store(2, out);
+      round_chunk(vb0, vb1, out);
+      stage_and_store(3, out);
     }
   }
 
