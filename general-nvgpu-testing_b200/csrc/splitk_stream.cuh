@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
       const int c_begin = kFold ? fold_half * 64 : 0;
       constexpr int kCols = kFold ? 64 : BN;     // columns this warp drains
       constexpr int kBoxes = kCols / 32;
-      constexpr int kBatch = 2;                  // boxes drained per round: 2 x 32 registers in flight
+      constexpr int kBatch = 2;                  // boxes drained per pass: 2 x 32 registers in flight
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + static_cast<uint32_t>(c_begin);
       const uint32_t stage_base = smem_base + quad * (kBoxes * 4096u);
       const uint32_t row_addr = lane * 128u;
@@ -241,18 +241,18 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
     const int n4 = p.n >> 2;
     // group sums: [kReduceGroups][2 * box_g units] float4 at the tail of the ring (the host keeps box_g <= 128)
     float4* sums = reinterpret_cast<float4*>(smem_gen + S::kRingBytes - S::kSumsBytes);
-    uint32_t round = 0;
-    for (long long gc = g0; gc < g1; gc += box_g, ++round) {
-      const int ng = static_cast<int>((g1 - gc < box_g) ? (g1 - gc) : box_g);  // granules of this round that are ours
+    uint32_t pass = 0;
+    for (long long gc = g0; gc < g1; gc += box_g, ++pass) {
+      const int ng = static_cast<int>((g1 - gc < box_g) ? (g1 - gc) : box_g);  // granules of this pass that are ours
       if (threadIdx.x == 0) {
         ptx::mbar_arrive_expect_tx(reduce_bar, box_bytes);
         ptx::tma_load_3d(smem_base, &p.tm_peer[0], reduce_bar, 0, static_cast<int>(gc), 0);
       }
       // every thread waits on the barrier itself (whoever sees the phase complete sees the copied bytes); the
       // verdict is made uniform so that nobody is left behind at a CTA barrier
-      const int landed = bounded_wait(reduce_bar, round & 1u, cta_abort, p.status, kFaultReduceWait) ? 1 : 0;
+      const int landed = bounded_wait(reduce_bar, pass & 1u, cta_abort, p.status, kFaultReduceWait) ? 1 : 0;
       if (!__syncthreads_and(landed)) break;
-      const int nu = 2 * ng;  // float4 units of this round
+      const int nu = 2 * ng;  // float4 units of this pass
       if (t < 128) {
         for (int u = q; u < nu; u += kReduceUnitsPerPass) {
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
         o.y = ptx::pack_half2(r.z, r.w);
         *reinterpret_cast<uint2*>(p.c + (unit / n4) * p.n + (unit % n4) * 4) = o;
       }
-      // the next round's copy overwrites what this round's loads read: generic reads before async writes
+      // the next pass's copy overwrites what this pass's loads read: generic reads before async writes
       ptx::fence_proxy_async_smem();
       __syncthreads();
     }
