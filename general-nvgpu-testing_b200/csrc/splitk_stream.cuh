@@ -221,7 +221,9 @@ __global__ void __launch_bounds__(192, 2) splitk_stream_kernel(const __grid_cons
 
   // ---- every CTA's partial is on its way to L2: meet, then sum.  All paths reach the barrier, including a CTA whose
   // bounded wait gave up (the fault word then tells the host that the result is invalid).
-  __threadfence();
+  // (No fence of our own here: the storing lanes have waited for their bulk stores to complete, and the grid barrier
+  // releases at GPU scope after a CTA barrier and acquires on the way out.  A __threadfence() by every thread in
+  // front of it cost 0.7 us per call.)
   cooperative_groups::this_grid().sync();
   {
     // The workspace is read back through a second tensor map that sees it as [planes][M * N / 8][8 floats]
